@@ -1,0 +1,84 @@
+// Shared helpers of the sm_100a kernels: element types, warp/block reductions and
+// the launch-status convention.
+//
+// Every launcher is an `extern "C"` function that takes raw device pointers, plain
+// integers and a stream, validates what it can on the host, launches, and returns a
+// cudaError_t-compatible int (0 = success, negative = an argument this build
+// refuses; the message is kept for llme_last_error()).  Launch errors are read with
+// cudaGetLastError() and never by synchronising the device, as the reference does in
+// src/runtime/kernels/cuda_kernels.cu:49-51.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LLME_API extern "C" __attribute__((visibility("default")))
+
+enum LlmeDType : int { LLME_F32 = 0, LLME_BF16 = 1 };
+
+// Error text of the last refused call in this thread.
+inline char* llme_error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+#include <stdio.h>
+#define LLME_REFUSE(...)                                              \
+    do {                                                              \
+        snprintf(llme_error_buffer(), 512, __VA_ARGS__);              \
+        return -1;                                                    \
+    } while (0)
+
+#define LLME_LAUNCH_STATUS()                                          \
+    do {                                                              \
+        cudaError_t e__ = cudaGetLastError();                         \
+        if (e__ != cudaSuccess) {                                     \
+            snprintf(llme_error_buffer(), 512, "%s", cudaGetErrorString(e__)); \
+        }                                                             \
+        return (int)e__;                                              \
+    } while (0)
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Sum over the 32 lanes; every lane gets the same value, and the order of additions
+// is fixed, so a result never depends on what else runs in the launch.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads (a multiple of 32); `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = (lane < nw) ? scratch[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = (lane < nw) ? scratch[lane] : -INFINITY;
+    return warp_max(t);
+}

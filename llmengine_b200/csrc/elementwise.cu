@@ -1,0 +1,265 @@
+// Memory-bound kernels of the layer body: embedding gather, RMS norm fused with the
+// residual add, per-head QK norm + rotary encoding + write into the paged cache, and
+// the SwiGLU gate.  All arithmetic is 32-bit; only storage may be bfloat16.
+//
+// Reference counterparts (src/runtime/kernels/cuda_kernels.cu): embedding_kernel
+// :380-397, rmsnorm_kernel :360-378 (also used as QK norm), add_kernel :224-227,
+// rope_kernel :430-450, swiglu_kernel :245-248, and the per-token cudaMemcpy cache
+// writes of src/runtime/cache/paged_kv_cache.cpp:189-207, which the fused write replaces.
+#include "common.cuh"
+
+LLME_API const char* llme_last_error() { return llme_error_buffer(); }
+
+// ----------------------------------------------------------------------------- embedding
+// out[t, :] = float(table[ids[t], :]).  An id outside the table gives a row of zeros here;
+// the engine refuses such ids on the host before it launches anything.
+template <typename W>
+__global__ void embedding_kernel(const int* __restrict__ ids, const W* __restrict__ table,
+                                 float* __restrict__ out, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * hidden;
+    if (id < 0 || id >= vocab) {
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = 0.0f;
+        return;
+    }
+    const W* row = table + (size_t)id * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = to_f32(row[j]);
+}
+
+LLME_API int llme_embedding(const int* ids, const void* table, int table_dtype, float* out,
+                            int tokens, int hidden, int vocab, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (!ids || !table || !out || hidden <= 0 || vocab <= 0) LLME_REFUSE("embedding: null pointer or non-positive size");
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == LLME_F32)
+        embedding_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+    else if (table_dtype == LLME_BF16)
+        embedding_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+    else
+        LLME_REFUSE("embedding: unsupported table dtype %d", table_dtype);
+    LLME_LAUNCH_STATUS();
+}
+
+// ----------------------------------------------------------------------------- RMS norm (+ residual add)
+// For output row i (source row r = rows ? rows[i] : i):
+//   v = x[r] (+ delta[r], stored back into x[r]);  y[i] = (v * 1/sqrt(mean(v^2) + eps)) * gain.
+// One block per row; the sum of squares is reduced in a fixed order.
+template <typename D, typename G, typename O, bool HAS_DELTA>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const D* __restrict__ delta, const G* __restrict__ gain,
+                               O* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* xr = x + (size_t)r * hidden;
+    const D* dr = HAS_DELTA ? delta + (size_t)r * hidden : nullptr;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float v = xr[j];
+        if (HAS_DELTA) {
+            v += to_f32(dr[j]);
+            xr[j] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    O* o = out + (size_t)i * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        // same thread wrote xr[j] above, so the re-read sees the sum
+        o[j] = from_f32<O>((xr[j] * rinv) * to_f32(gain[j]));
+    }
+}
+
+template <typename D, typename G, typename O, bool HAS_DELTA>
+static void launch_rmsnorm(float* x, const void* delta, const void* gain, void* out, const int* rows,
+                           int n_out, int hidden, float eps, cudaStream_t s) {
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    rmsnorm_kernel<D, G, O, HAS_DELTA><<<n_out, threads, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+}
+
+template <typename D, bool HAS_DELTA>
+static int dispatch_rmsnorm(float* x, const void* delta, const void* gain, int gain_dtype, void* out, int out_dtype,
+                            const int* rows, int n_out, int hidden, float eps, cudaStream_t s) {
+    if (gain_dtype == LLME_F32 && out_dtype == LLME_F32) launch_rmsnorm<D, float, float, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s);
+    else if (gain_dtype == LLME_F32 && out_dtype == LLME_BF16) launch_rmsnorm<D, float, __nv_bfloat16, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s);
+    else if (gain_dtype == LLME_BF16 && out_dtype == LLME_F32) launch_rmsnorm<D, __nv_bfloat16, float, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s);
+    else if (gain_dtype == LLME_BF16 && out_dtype == LLME_BF16) launch_rmsnorm<D, __nv_bfloat16, __nv_bfloat16, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s);
+    else LLME_REFUSE("rmsnorm: unsupported gain/out dtype %d/%d", gain_dtype, out_dtype);
+    LLME_LAUNCH_STATUS();
+}
+
+// x [*, hidden] 32-bit (updated in place when delta is given); delta nullable; rows nullable
+// (n_out source-row indices); out [n_out, hidden].
+LLME_API int llme_rmsnorm(float* x, const void* delta, int delta_dtype, const void* gain, int gain_dtype,
+                          void* out, int out_dtype, const int* rows, int n_out, int hidden, float eps,
+                          cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    if (!x || !gain || !out || hidden <= 0) LLME_REFUSE("rmsnorm: null pointer or non-positive size");
+    if (!(eps > 0.0f)) LLME_REFUSE("rmsnorm: eps must be positive");
+    if (!delta) return dispatch_rmsnorm<float, false>(x, nullptr, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream);
+    if (delta_dtype == LLME_F32) return dispatch_rmsnorm<float, true>(x, delta, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream);
+    if (delta_dtype == LLME_BF16) return dispatch_rmsnorm<__nv_bfloat16, true>(x, delta, gain, gain_dtype, out, out_dtype, rows, n_out, hidden, eps, stream);
+    LLME_REFUSE("rmsnorm: unsupported delta dtype %d", delta_dtype);
+}
+
+// ----------------------------------------------------------------------------- QK norm + rotary + cache write
+// One warp per (token, head).  Heads 0..nh-1 are query heads, then nkv key heads, then nkv
+// value heads.  Query and key heads: optional RMS norm over head_dim (gain shared by all
+// heads), optional rotation of the pairs (d, d + head_dim/2) with cos/sin read from a table
+// row chosen by the token's position.  Queries go to q_out, keys to k_out and/or the cache,
+// values to the cache.  Cache layout: [page][K|V][kv head][slot in page][head_dim]; a token's
+// place is slot_mapping[t] = page * page_size + slot, negative = not stored.
+struct QkvArgs {
+    const void* q_in; const void* k_in; const void* v_in;
+    long long q_stride, k_stride, v_stride;      // elements between consecutive tokens
+    const void* q_gain; const void* k_gain;       // nullable: no norm
+    int gain_dtype;
+    float eps;
+    const float* cos_sin;                         // nullable: no rotation; [max_pos, head_dim] = cos | sin
+    const int* positions;
+    int max_positions;
+    void* q_out; void* k_out;                     // nullable; [T, nh*hd], [T, nkv*hd]
+    void* cache; const int* slot_mapping;         // nullable
+    int tokens, nh, nkv, hd, page_size;
+};
+
+template <typename I, typename O, typename G>
+__global__ void qkv_post_kernel(QkvArgs a) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int heads = a.nh + 2 * a.nkv;
+    if (wid >= (long long)a.tokens * heads) return;
+    const int t = (int)(wid / heads);
+    const int h = (int)(wid % heads);
+    const int hd = a.hd, half = hd >> 1;
+
+    if (h >= a.nh + a.nkv) {                       // value head: copy into the cache
+        if (!a.cache || !a.v_in) return;
+        const int slot = a.slot_mapping[t];
+        if (slot < 0) return;
+        const int kvh = h - a.nh - a.nkv;
+        const I* src = (const I*)a.v_in + (size_t)t * a.v_stride + (size_t)kvh * hd;
+        const int page = slot / a.page_size, off = slot % a.page_size;
+        O* dst = (O*)a.cache + ((((size_t)page * 2 + 1) * a.nkv + kvh) * a.page_size + off) * hd;
+        for (int d = lane; d < hd; d += 32) dst[d] = from_f32<O>(to_f32(src[d]));
+        return;
+    }
+
+    const bool is_q = h < a.nh;
+    const int head = is_q ? h : h - a.nh;
+    const I* src;
+    if (is_q) {
+        if (!a.q_in) return;
+        src = (const I*)a.q_in + (size_t)t * a.q_stride + (size_t)head * hd;
+    } else {
+        if (!a.k_in) return;
+        src = (const I*)a.k_in + (size_t)t * a.k_stride + (size_t)head * hd;
+    }
+    const G* gain = (const G*)(is_q ? a.q_gain : a.k_gain);
+
+    float rinv = 1.0f;
+    if (gain) {
+        float ss = 0.0f;
+        for (int d = lane; d < hd; d += 32) {
+            const float v = to_f32(src[d]);
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        rinv = 1.0f / sqrtf(ss / (float)hd + a.eps);
+    }
+
+    O* q_dst = (is_q && a.q_out) ? (O*)a.q_out + ((size_t)t * a.nh + head) * hd : nullptr;
+    O* k_dst = (!is_q && a.k_out) ? (O*)a.k_out + ((size_t)t * a.nkv + head) * hd : nullptr;
+    O* c_dst = nullptr;
+    if (!is_q && a.cache) {
+        const int slot = a.slot_mapping[t];
+        if (slot >= 0) {
+            const int page = slot / a.page_size, off = slot % a.page_size;
+            c_dst = (O*)a.cache + ((((size_t)page * 2 + 0) * a.nkv + head) * a.page_size + off) * hd;
+        }
+    }
+    const float* cs = nullptr;
+    if (a.cos_sin) {
+        int pos = a.positions[t];
+        pos = pos < 0 ? 0 : (pos >= a.max_positions ? a.max_positions - 1 : pos);   // the host refuses such positions
+        cs = a.cos_sin + (size_t)pos * hd;
+    }
+    for (int d = lane; d < half; d += 32) {
+        float x0 = to_f32(src[d]), x1 = to_f32(src[d + half]);
+        if (gain) {
+            x0 = (x0 * rinv) * to_f32(gain[d]);
+            x1 = (x1 * rinv) * to_f32(gain[d + half]);
+        }
+        float y0 = x0, y1 = x1;
+        if (cs) {
+            const float c = cs[d], s = cs[half + d];
+            y0 = x0 * c - x1 * s;
+            y1 = x0 * s + x1 * c;
+        }
+        const O o0 = from_f32<O>(y0), o1 = from_f32<O>(y1);
+        if (q_dst) { q_dst[d] = o0; q_dst[d + half] = o1; }
+        if (k_dst) { k_dst[d] = o0; k_dst[d + half] = o1; }
+        if (c_dst) { c_dst[d] = o0; c_dst[d + half] = o1; }
+    }
+}
+
+template <typename I, typename O>
+static int dispatch_qkv_gain(const QkvArgs& a, cudaStream_t s) {
+    const long long warps = (long long)a.tokens * (a.nh + 2 * a.nkv);
+    const int wpb = 8;
+    const long long blocks = (warps + wpb - 1) / wpb;
+    if (blocks > 2147483647LL) LLME_REFUSE("qkv_post: too many (token, head) pairs for one launch");
+    if (a.gain_dtype == LLME_F32) qkv_post_kernel<I, O, float><<<(unsigned)blocks, wpb * 32, 0, s>>>(a);
+    else if (a.gain_dtype == LLME_BF16) qkv_post_kernel<I, O, __nv_bfloat16><<<(unsigned)blocks, wpb * 32, 0, s>>>(a);
+    else LLME_REFUSE("qkv_post: unsupported gain dtype %d", a.gain_dtype);
+    LLME_LAUNCH_STATUS();
+}
+
+LLME_API int llme_qkv_post(const QkvArgs* args, int in_dtype, int out_dtype, cudaStream_t stream) {
+    const QkvArgs& a = *args;
+    if (a.tokens <= 0) return 0;
+    if (a.nh < 0 || a.nkv < 0 || a.hd <= 0 || (a.hd & 1)) LLME_REFUSE("qkv_post: head_dim must be positive and even, got %d", a.hd);
+    if (a.cache && (!a.slot_mapping || a.page_size <= 0)) LLME_REFUSE("qkv_post: a cache needs slot_mapping and page_size");
+    if (a.cos_sin && (!a.positions || a.max_positions <= 0)) LLME_REFUSE("qkv_post: rotation needs positions");
+    if ((a.q_gain || a.k_gain) && !(a.eps > 0.0f)) LLME_REFUSE("qkv_post: eps must be positive");
+    if (in_dtype == LLME_F32 && out_dtype == LLME_F32) return dispatch_qkv_gain<float, float>(a, stream);
+    if (in_dtype == LLME_BF16 && out_dtype == LLME_BF16) return dispatch_qkv_gain<__nv_bfloat16, __nv_bfloat16>(a, stream);
+    if (in_dtype == LLME_F32 && out_dtype == LLME_BF16) return dispatch_qkv_gain<float, __nv_bfloat16>(a, stream);
+    if (in_dtype == LLME_BF16 && out_dtype == LLME_F32) return dispatch_qkv_gain<__nv_bfloat16, float>(a, stream);
+    LLME_REFUSE("qkv_post: unsupported in/out dtype %d/%d", in_dtype, out_dtype);
+}
+
+// ----------------------------------------------------------------------------- SwiGLU
+// in [T, 2*inter] = gate | up;  out[t, i] = gate / (1 + exp(-gate)) * up.
+template <typename I, typename O>
+__global__ void swiglu_kernel(const I* __restrict__ in, O* __restrict__ out, long long total, int inter) {
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const long long t = idx / inter;
+        const int i = (int)(idx - t * inter);
+        const float g = to_f32(in[t * 2 * inter + i]);
+        const float u = to_f32(in[t * 2 * inter + inter + i]);
+        out[idx] = from_f32<O>((g / (1.0f + expf(-g))) * u);
+    }
+}
+
+LLME_API int llme_swiglu(const void* in, int in_dtype, void* out, int out_dtype, int tokens, int inter,
+                         cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (!in || !out || inter <= 0) LLME_REFUSE("swiglu: null pointer or non-positive size");
+    const long long total = (long long)tokens * inter;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (in_dtype == LLME_F32 && out_dtype == LLME_F32)
+        swiglu_kernel<float, float><<<(unsigned)blocks, 256, 0, stream>>>((const float*)in, (float*)out, total, inter);
+    else if (in_dtype == LLME_BF16 && out_dtype == LLME_BF16)
+        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, inter);
+    else if (in_dtype == LLME_F32 && out_dtype == LLME_BF16)
+        swiglu_kernel<float, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, total, inter);
+    else
+        LLME_REFUSE("swiglu: unsupported in/out dtype %d/%d", in_dtype, out_dtype);
+    LLME_LAUNCH_STATUS();
+}

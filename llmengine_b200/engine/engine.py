@@ -1,0 +1,264 @@
+"""The step function: one call runs one batch of (request, its next tokens) through the model,
+from the cache that earlier steps left, and returns the logits at the wanted places.
+
+The reference's Executor::run serves one sequence per run with a fixed token count
+(src/runtime/executor.cpp:45-77) and advances the cache length once per run, after all
+layers (src/runtime/runtime_context.cpp:222-243; the paged path latches the write position in
+src/runtime/kernels/cpu_kernel_adapter.cpp:482-492).  `Engine.step` keeps those rules — every
+layer of a step writes at the same positions, lengths move once per step — for a batch that
+mixes prompt portions of some requests with single decoded tokens of others.
+
+The engine has no policy: which requests run, how prompts are cut and when requests end is
+decided by the caller (the scheduler, or a trace).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheError, CacheManager, OutOfPages
+from ..config import EngineConfig, config_from_dict, load_config
+from ..parts.base import PagedKVSpec, Runtime, StateSpec
+from ..weights import load_model_weights, random_model_weights
+from .batch import GroupView, PagedKVView, StateView, StepBatch
+from .model import Model
+
+
+class StepError(ValueError):
+    """The batch was refused; no state was changed."""
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them (0-based,
+    within `tokens`) whose logits are wanted."""
+
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class Engine:
+    def __init__(self, model_dir: Optional[str] = None, *, config=None, random_seed: Optional[int] = None,
+                 engine_config: Optional[EngineConfig] = None, ops=None):
+        """`model_dir`: a folder with config.json and model.safetensors.  Or `config` (a typed
+        configuration, or a dict of config.json keys) with `random_seed` for random weights made
+        on the device.  `ops` replaces the CUDA kernel set (tests of the host logic only)."""
+        self.ec = ec = engine_config or EngineConfig()
+        if model_dir is not None:
+            self.config = load_config(model_dir)
+        elif config is not None:
+            self.config = config_from_dict(config) if isinstance(config, dict) else config
+        else:
+            raise ValueError("Engine needs a model folder or a configuration")
+        self.device = torch.device(ec.device)
+        self.dtype = torch.bfloat16 if ec.dtype == "bfloat16" else torch.float32
+        if ops is None:
+            from ..kernels.ops import CudaOps
+            ops = CudaOps(self.device)
+        self.ops = ops
+        self.spec = self.config.model_spec()
+        self.max_model_len = min(ec.max_model_len or self.spec.max_positions, self.spec.max_positions)
+        self.rt = Runtime(ops, self.device, self.dtype, ec.max_num_batched_tokens, ec.kernels)
+        self.model = Model(self.spec, self.rt)
+        if model_dir is not None:
+            load_model_weights(self.model, self.config, model_dir, self.dtype, self.device)
+        else:
+            if random_seed is None:
+                raise ValueError("a configuration without a model folder needs random_seed")
+            random_model_weights(self.model, random_seed, self.dtype, self.device)
+        self.vocab_size = self.spec.vocab_size
+
+        specs = self.model.cache_specs()
+        tokens = ec.max_cached_tokens or self._tokens_from_free_memory(specs)
+        self.cache = CacheManager(specs, ec.page_size, tokens, ec.max_num_seqs, self.max_model_len)
+        self.cache.allocate_device(self.dtype, self.device)
+        self._caches = []
+        for i, (spec, cache_from) in enumerate(specs):
+            owner = self.cache.run_owner[i]
+            if isinstance(spec, PagedKVSpec):
+                self._caches.append(PagedKVView(self.cache.kv[owner], self.cache.run_group[i], cache_from is None))
+            elif isinstance(spec, StateSpec):
+                self._caches.append(StateView(self.cache.state[owner]))
+            else:
+                self._caches.append(None)
+        self._init_metadata()
+        self.steps = 0
+
+    # ------------------------------------------------------------------ sizing
+    def _tokens_from_free_memory(self, specs) -> int:
+        per_token = 0
+        size = 2 if self.dtype == torch.bfloat16 else 4
+        for s, c in specs:
+            if isinstance(s, PagedKVSpec) and c is None:
+                per_token += 2 * s.num_kv_heads * s.head_dim * size
+        if per_token == 0:
+            return self.ec.page_size
+        if self.device.type != "cuda":
+            return self.ec.max_num_seqs * min(self.max_model_len, 4096)
+        free, _ = torch.cuda.mem_get_info(self.device)
+        # leave room for the step's workspace: roughly 64 bytes per hidden value of each token of the budget
+        workspace = self.ec.max_num_batched_tokens * self.spec.hidden_size * 64 + (2 << 30)
+        usable = max(0, int(free * self.ec.gpu_memory_fraction) - workspace)
+        tokens = usable // per_token
+        cap = self.ec.max_num_seqs * self.max_model_len
+        tokens = min(tokens, cap)
+        if tokens < self.ec.page_size:
+            raise CacheError("no device memory is left for the cache after the weights")
+        return int(tokens)
+
+    # ------------------------------------------------------------------ step metadata
+    def _init_metadata(self) -> None:
+        T, R, G = self.ec.max_num_batched_tokens, self.ec.max_num_seqs, len(self.cache.groups)
+        self._T_cap, self._R_cap = T, R
+        names = ["token_ids", "positions", "token_request", "logit_rows"] + [f"slot_mapping{g}" for g in range(G)]
+        self._off: Dict[str, slice] = {}
+        o = 0
+        for n in names:
+            self._off[n] = slice(o, o + T)
+            o += T
+        for n, ln in (("cu_q_lens", R + 1), ("ctx_lens", R), ("state_slots", R), ("first_portion", R)):
+            self._off[n] = slice(o, o + ln)
+            o += ln
+        self._meta_len = o
+        pin = self.device.type == "cuda"
+        self._staging = [torch.zeros(o, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._staging_np = [s.numpy() for s in self._staging]
+        self._staging_ev = [torch.cuda.Event() if pin else None for _ in range(2)]
+        self._staging_used = [False, False]
+        self._meta_dev = torch.zeros(o, dtype=torch.int32, device=self.device)
+
+    def _build_batch(self, entries: List[StepEntry], starts: List[int]) -> StepBatch:
+        i = self.steps & 1
+        if self._staging_ev[i] is not None and self._staging_used[i]:
+            self._staging_ev[i].synchronize()
+        h = self._staging_np[i]
+        off = self._off
+        q_lens = [len(e.tokens) for e in entries]
+        T, R = sum(q_lens), len(entries)
+        cu = np.zeros(R + 1, dtype=np.int32)
+        cu[1:] = np.cumsum(q_lens)
+        tok = h[off["token_ids"]]
+        pos = h[off["positions"]]
+        treq = h[off["token_request"]]
+        rows: List[int] = []
+        for r, (e, s) in enumerate(zip(entries, starts)):
+            a, b = int(cu[r]), int(cu[r + 1])
+            st = self.cache.requests[e.request]
+            tok[a:b] = np.asarray(e.tokens, dtype=np.int32)
+            pos[a:b] = np.arange(s, s + (b - a), dtype=np.int32)
+            treq[a:b] = st.slot
+            for g in range(len(self.cache.groups)):
+                h[off[f"slot_mapping{g}"]][a:b] = self.cache.slot_mapping(e.request, g, s, b - a)
+            rows.extend(a + int(w) for w in e.want)
+            h[off["ctx_lens"]][r] = s + (b - a)
+            h[off["state_slots"]][r] = st.slot
+            h[off["first_portion"]][r] = 1 if s == 0 else 0
+        h[off["cu_q_lens"]][: R + 1] = cu
+        NL = len(rows)
+        h[off["logit_rows"]][:NL] = np.asarray(rows, dtype=np.int32) if NL else 0
+        self._meta_dev.copy_(self._staging[i], non_blocking=True)
+        if self._staging_ev[i] is not None:
+            self._staging_ev[i].record()
+            self._staging_used[i] = True
+        d = self._meta_dev
+
+        def view(name: str, n: int) -> torch.Tensor:
+            s = off[name]
+            return d[s.start:s.start + n]
+
+        groups = [GroupView(g.page_size, g.window, self.cache.tables_dev[gi], view(f"slot_mapping{gi}", T), g.max_blocks)
+                  for gi, g in enumerate(self.cache.groups)]
+        return StepBatch(
+            num_tokens=T, num_requests=R, q_lens=q_lens, start_positions=list(starts),
+            token_ids=view("token_ids", T), positions=view("positions", T), token_request=view("token_request", T),
+            cu_q_lens=view("cu_q_lens", R + 1), ctx_lens=view("ctx_lens", R), state_slots=view("state_slots", R),
+            first_portion=view("first_portion", R), logit_rows=view("logit_rows", NL), groups=groups)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry], end: Sequence[Hashable] = ()) -> Optional[torch.Tensor]:
+        """Run the entries' tokens as one batch.  Returns 32-bit logits [wanted, vocab] on the device,
+        in the order of the entries and of their `want` lists (None if nothing is wanted); the tensor
+        is overwritten by the next step.  Requests named in `end` give back what they hold after the
+        step.  A request is created by its first entry.  A refused batch changes nothing."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        seen = set()
+        total = 0
+        for e in entries:
+            if e.request in seen:
+                raise StepError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            n = len(e.tokens)
+            total += n
+            toks = np.asarray(e.tokens)
+            if toks.ndim != 1 or not np.issubdtype(toks.dtype, np.integer):
+                raise StepError(f"request {e.request!r}: tokens must be a flat list of integers")
+            if toks.min() < 0 or toks.max() >= self.vocab_size:
+                # the reference's CPU embedding refuses such ids too (src/runtime/kernels/cpu_kernel_adapter.cpp:73-78)
+                raise StepError(f"request {e.request!r}: a token id is outside the vocabulary [0, {self.vocab_size})")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
+        for r in end:
+            if r not in seen and not self.cache.has(r):
+                raise StepError(f"request {r!r} is ended but is not live")
+        if total > self._T_cap:
+            raise StepError(f"the step has {total} tokens, the budget is {self._T_cap} (max_num_batched_tokens)")
+        if len(entries) > self._R_cap:
+            raise StepError(f"the step has {len(entries)} requests, the limit is {self._R_cap} (max_num_seqs)")
+        starts = []
+        for e in entries:
+            s = self.cache.length(e.request) if self.cache.has(e.request) else 0
+            if s + len(e.tokens) > self.max_model_len:
+                raise StepError(f"request {e.request!r} would reach {s + len(e.tokens)} tokens, "
+                                f"the model's limit is {self.max_model_len}")
+            starts.append(s)
+
+        # reserve: new requests and pages, undone together if anything is short
+        created = []
+        grown = []
+        try:
+            for e, s in zip(entries, starts):
+                if not self.cache.has(e.request):
+                    self.cache.add_request(e.request)
+                    created.append(e.request)
+                before = [len(b) for b in self.cache.requests[e.request].blocks]
+                self.cache.reserve(e.request, s + len(e.tokens))
+                grown.append((e.request, before))
+        except (OutOfPages, CacheError) as err:
+            self._undo(created, grown)
+            raise StepError(f"the step does not fit the cache: {err}") from None
+
+        logits = None
+        if entries:
+            batch = self._build_batch(list(entries), starts)
+            self.cache.flush()
+            logits = self.model.forward(batch, self._caches)
+            for e, s in zip(entries, starts):
+                self.cache.advance(e.request, s + len(e.tokens))
+            self.steps += 1
+        for r in end:
+            self.cache.free_request(r)
+        return logits
+
+    def _undo(self, created, grown) -> None:
+        for req, before in grown:
+            if req in created:
+                continue
+            st = self.cache.requests[req]
+            for gi, n in enumerate(before):
+                extra = st.blocks[gi][n:]
+                if extra:
+                    self.cache.groups[gi].pool.free([p for p in extra if p >= 0])
+                    del st.blocks[gi][n:]
+                    self.cache.tables[gi][st.slot, n:n + len(extra)] = -1
+                    self.cache._mark(gi, st.slot, n, n + len(extra))
+        for req in created:
+            self.cache.free_request(req)
+
+    def free(self, request: Hashable) -> None:
+        self.cache.free_request(request)

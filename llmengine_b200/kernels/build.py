@@ -1,0 +1,126 @@
+"""Compiling the CUDA sources of `csrc/` for sm_100a into shared libraries, one
+per source file, inside the package folder.
+
+Each library is built the first time something needs it, so a run compiles only
+what its model and dtype use; `build_all()` compiles everything (used by the
+"does it build" check, which needs no GPU because nvcc cross-compiles).  A
+library's file name carries a hash of its source, the shared header and the
+flags, so a changed source never loads a stale binary.  While nvcc runs, a line
+is printed every few seconds.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+from typing import Dict, Iterable, List, Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
+
+# library name -> source file
+SOURCES: Dict[str, str] = {
+    "elementwise": "elementwise.cu",
+    "attention_plain": "attention_plain.cu",
+    "gemm_f32": "gemm_f32.cu",
+    "sampling": "sampling.cu",
+}
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+    "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+]
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def _log(msg: str) -> None:
+    print(f"[llmengine_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("LLMENGINE_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise BuildError("nvcc was not found (looked at $LLMENGINE_NVCC, PATH and /usr/local/cuda/bin); "
+                     "the kernels of this engine have to be compiled for sm_100a")
+
+
+def build_dir() -> str:
+    """`<package>/_build` when it can be written, else a per-user folder under the temp dir."""
+    d = os.path.join(os.path.dirname(_HERE), "_build")
+    try:
+        os.makedirs(d, exist_ok=True)
+        probe = os.path.join(d, f".w{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.unlink(probe)
+        return d
+    except OSError:
+        d = os.path.join(tempfile.gettempdir(), f"llmengine_b200_build_{os.getuid()}")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+
+def _digest(name: str) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for fn in sorted(os.listdir(CSRC)):
+        if fn.endswith((".cuh", ".h")) or fn == SOURCES[name]:
+            with open(os.path.join(CSRC, fn), "rb") as f:
+                h.update(fn.encode())
+                h.update(f.read())
+    return h.hexdigest()[:12]
+
+
+def library_path(name: str) -> str:
+    if name not in SOURCES:
+        raise BuildError(f"no kernel library named {name!r}; known: {', '.join(sorted(SOURCES))}")
+    return os.path.join(build_dir(), f"llme_{name}_{_digest(name)}.so")
+
+
+def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) -> Dict[str, str]:
+    """Compile the named libraries that are not built yet (in parallel) and return their paths."""
+    names = list(dict.fromkeys(names))
+    paths = {n: library_path(n) for n in names}
+    todo = [n for n in names if not os.path.exists(paths[n])]
+    if not todo:
+        return paths
+    nvcc = find_nvcc()
+    procs = {}
+    t0 = time.time()
+    for n in todo:
+        tmp = f"{paths[n]}.{os.getpid()}.tmp"
+        cmd = [nvcc, *NVCC_FLAGS, *(extra_flags or []), "-I", CSRC, "-o", tmp, os.path.join(CSRC, SOURCES[n])]
+        _log(f"compiling {SOURCES[n]} for sm_100a ...")
+        procs[n] = (subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True), tmp)
+    last = time.time()
+    pending = dict(procs)
+    while pending:
+        for n, (p, tmp) in list(pending.items()):
+            if p.poll() is None:
+                continue
+            out = p.stdout.read() if p.stdout else ""
+            del pending[n]
+            if p.returncode != 0:
+                for _, (q, qtmp) in pending.items():
+                    q.kill()
+                raise BuildError(f"nvcc failed on {SOURCES[n]} (exit {p.returncode}):\n{out}")
+            os.replace(tmp, paths[n])
+            _log(f"built {os.path.basename(paths[n])} in {time.time() - t0:.0f} s")
+        if pending:
+            time.sleep(0.2)
+            if time.time() - last > 8:
+                last = time.time()
+                _log(f"still compiling {', '.join(sorted(pending))} ({last - t0:.0f} s)")
+    return paths
+
+
+def build_all() -> Dict[str, str]:
+    return ensure_built(list(SOURCES))

@@ -1,0 +1,233 @@
+"""Python face of the CUDA kernels: loads the compiled libraries and launches
+their `extern "C"` entry points on torch tensors, on torch's current stream.
+
+There is no fallback: without a CUDA device, or if a library cannot be compiled
+or loaded, `CudaOps` raises `KernelsUnavailable`.  The only library matrix
+product is the bfloat16 `linear`, which goes to cuBLAS through `torch.mm` (the
+reference also hands its dense products to cuBLAS:
+src/runtime/kernels/cuda_kernels.cu:892-908); the 32-bit `linear` runs this
+package's own FMA kernel.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_char_p, c_float, c_int, c_longlong, c_void_p
+from typing import Dict, Optional
+
+import torch
+
+from . import build
+
+
+class KernelsUnavailable(RuntimeError):
+    pass
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_F32, _BF16 = 0, 1
+
+
+def _code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return _F32
+    if dt == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dt}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class _QkvArgs(Structure):
+    _fields_ = [
+        ("q_in", c_void_p), ("k_in", c_void_p), ("v_in", c_void_p),
+        ("q_stride", c_longlong), ("k_stride", c_longlong), ("v_stride", c_longlong),
+        ("q_gain", c_void_p), ("k_gain", c_void_p), ("gain_dtype", c_int), ("eps", c_float),
+        ("cos_sin", c_void_p), ("positions", c_void_p), ("max_positions", c_int),
+        ("q_out", c_void_p), ("k_out", c_void_p), ("cache", c_void_p), ("slot_mapping", c_void_p),
+        ("tokens", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("page_size", c_int),
+    ]
+
+
+class _AttnArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("cache", c_void_p), ("out", c_void_p), ("positions", c_void_p),
+        ("token_request", c_void_p), ("block_tables", c_void_p), ("max_blocks", c_int),
+        ("tokens", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("page_size", c_int),
+        ("window", c_int), ("scale", c_float),
+    ]
+
+
+class _SampleArgs(Structure):
+    _fields_ = [
+        ("logits", c_void_p), ("ld", c_longlong), ("rows", c_int), ("vocab", c_int),
+        ("greedy", c_void_p), ("temperature", c_void_p), ("top_k", c_void_p), ("top_p", c_void_p),
+        ("u", c_void_p), ("out", c_void_p),
+    ]
+
+
+class CudaOps:
+    """The kernel set the parts compute with.  One instance per engine."""
+
+    def __init__(self, device: torch.device):
+        if not torch.cuda.is_available():
+            raise KernelsUnavailable(
+                "no CUDA device is visible: this engine runs only on a GPU (sm_100a) and has no CPU fallback")
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise KernelsUnavailable(f"device {device} is not a CUDA device")
+        self._libs: Dict[str, ctypes.CDLL] = {}
+        self.launches = 0          # kernels of this package launched so far (cuBLAS calls are not counted)
+
+    # ------------------------------------------------------------------ loading
+    def require(self, *names: str) -> None:
+        """Compile (if needed) and load the named libraries."""
+        missing = [n for n in names if n not in self._libs]
+        if not missing:
+            return
+        try:
+            paths = build.ensure_built(missing)
+        except build.BuildError as e:
+            raise KernelsUnavailable(str(e)) from None
+        for n in missing:
+            try:
+                lib = ctypes.CDLL(paths[n])
+            except OSError as e:
+                raise KernelsUnavailable(f"cannot load {paths[n]}: {e}") from None
+            lib.llme_last_error.restype = c_char_p
+            self._libs[n] = lib
+
+    def _lib(self, name: str) -> ctypes.CDLL:
+        lib = self._libs.get(name)
+        if lib is None:
+            self.require(name)
+            lib = self._libs[name]
+        return lib
+
+    def _check(self, lib: ctypes.CDLL, rc: int, what: str) -> None:
+        self.launches += 1
+        if rc != 0:
+            msg = lib.llme_last_error().decode("utf-8", "replace")
+            raise KernelError(f"{what}: {msg} (code {rc})")
+
+    @staticmethod
+    def _stream() -> c_void_p:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # ------------------------------------------------------------------ kernels
+    def embedding(self, ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        lib = self._lib("elementwise")
+        assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous() and out.is_contiguous()
+        rc = lib.llme_embedding(c_void_p(ids.data_ptr()), c_void_p(table.data_ptr()), c_int(_code(table.dtype)),
+                                c_void_p(out.data_ptr()), c_int(ids.numel()), c_int(table.shape[1]),
+                                c_int(table.shape[0]), self._stream())
+        self._check(lib, rc, "embedding")
+        return out
+
+    def rmsnorm(self, x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+                delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        lib = self._lib("elementwise")
+        assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+        assert delta is None or (delta.is_contiguous() and delta.shape == x.shape)
+        n_out = out.shape[0]
+        assert (rows.numel() if rows is not None else x.shape[0]) == n_out
+        rc = lib.llme_rmsnorm(c_void_p(x.data_ptr()), c_void_p(_ptr(delta)),
+                              c_int(_code(delta.dtype) if delta is not None else 0),
+                              c_void_p(gain.data_ptr()), c_int(_code(gain.dtype)),
+                              c_void_p(out.data_ptr()), c_int(_code(out.dtype)), c_void_p(_ptr(rows)),
+                              c_int(n_out), c_int(x.shape[1]), c_float(eps), self._stream())
+        self._check(lib, rc, "rmsnorm")
+        return out
+
+    def qkv_post(self, *, q_in, k_in, v_in, num_heads: int, num_kv_heads: int, head_dim: int,
+                 q_gain=None, k_gain=None, eps: float = 0.0, cos_sin=None, positions=None,
+                 q_out=None, k_out=None, cache=None, slot_mapping=None, page_size: int = 0) -> None:
+        """QK norm, rotation and cache write for `tokens` rows; see csrc/elementwise.cu."""
+        lib = self._lib("elementwise")
+        ref = q_in if q_in is not None else (k_in if k_in is not None else v_in)
+        tokens = ref.shape[0]
+        outs = [t for t in (q_out, k_out, cache) if t is not None]
+        if not outs:
+            return
+        out_dtype = outs[0].dtype
+        assert all(t.dtype == out_dtype for t in outs)
+        for t in (q_in, k_in, v_in):
+            assert t is None or (t.dtype == ref.dtype and t.stride(-1) == 1)
+        gains = [g for g in (q_gain, k_gain) if g is not None]
+        assert all(g.dtype == gains[0].dtype for g in gains)
+        a = _QkvArgs(
+            _ptr(q_in), _ptr(k_in), _ptr(v_in),
+            q_in.stride(0) if q_in is not None else 0, k_in.stride(0) if k_in is not None else 0,
+            v_in.stride(0) if v_in is not None else 0,
+            _ptr(q_gain), _ptr(k_gain), _code(gains[0].dtype) if gains else 0, eps,
+            _ptr(cos_sin), _ptr(positions), cos_sin.shape[0] if cos_sin is not None else 0,
+            _ptr(q_out), _ptr(k_out), _ptr(cache), _ptr(slot_mapping),
+            tokens, num_heads, num_kv_heads, head_dim, page_size)
+        rc = lib.llme_qkv_post(byref(a), c_int(_code(ref.dtype)), c_int(_code(out_dtype)), self._stream())
+        self._check(lib, rc, "qkv_post")
+
+    def attention_plain(self, *, q, cache, out, positions, token_request, block_tables, num_heads: int,
+                        num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float) -> torch.Tensor:
+        lib = self._lib("attention_plain")
+        assert q.dtype == cache.dtype == out.dtype and q.is_contiguous() and out.is_contiguous()
+        assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+        a = _AttnArgs(q.data_ptr(), cache.data_ptr(), out.data_ptr(), positions.data_ptr(), token_request.data_ptr(),
+                      block_tables.data_ptr(), block_tables.shape[1], q.shape[0], num_heads, num_kv_heads, head_dim,
+                      page_size, window, scale)
+        rc = lib.llme_attention_plain(byref(a), c_int(_code(q.dtype)), self._stream())
+        self._check(lib, rc, "attention_plain")
+        return out
+
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        lib = self._lib("elementwise")
+        assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.shape[1] == 2 * out.shape[1]
+        rc = lib.llme_swiglu(c_void_p(gate_up.data_ptr()), c_int(_code(gate_up.dtype)), c_void_p(out.data_ptr()),
+                             c_int(_code(out.dtype)), c_int(out.shape[0]), c_int(out.shape[1]), self._stream())
+        self._check(lib, rc, "swiglu")
+        return out
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out[M,N] = x[M,K] @ w[N,K]^T.  32-bit operands: this package's FMA kernel (never a
+        reduced-precision mode).  bfloat16 operands: cuBLAS with 32-bit accumulation, the output
+        in `out`'s type."""
+        M, K = x.shape
+        N = w.shape[0]
+        assert w.shape[1] == K and out.shape == (M, N)
+        if x.dtype == torch.float32:
+            lib = self._lib("gemm_f32")
+            assert out.dtype == torch.float32 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+            rc = lib.llme_gemm_nt_f32(c_void_p(x.data_ptr()), c_void_p(w.data_ptr()), c_int(_code(w.dtype)),
+                                      c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
+                                      c_longlong(x.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                                      self._stream())
+            self._check(lib, rc, "gemm_f32")
+            return out
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        if M == 0:
+            return out
+        if out.dtype == torch.bfloat16:
+            torch.mm(x, w.t(), out=out)
+        else:
+            torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+        return out
+
+    def repetition_penalty(self, logits, rows, tokens, counts, penalty) -> None:
+        lib = self._lib("sampling")
+        rc = lib.llme_repetition_penalty(c_void_p(logits.data_ptr()), c_longlong(logits.stride(0)),
+                                         c_void_p(rows.data_ptr()), c_void_p(tokens.data_ptr()),
+                                         c_void_p(counts.data_ptr()), c_void_p(penalty.data_ptr()),
+                                         c_int(rows.numel()), c_int(logits.shape[1]), self._stream())
+        self._check(lib, rc, "repetition_penalty")
+
+    def sample(self, logits: torch.Tensor, *, greedy, temperature, top_k, top_p, u, out: torch.Tensor) -> torch.Tensor:
+        lib = self._lib("sampling")
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+        a = _SampleArgs(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(greedy),
+                        _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(u), out.data_ptr())
+        rc = lib.llme_sample(byref(a), self._stream())
+        self._check(lib, rc, "sample")
+        return out

@@ -1,0 +1,132 @@
+"""Binding weights to a model by tensor name, from a model folder or from a seed.
+
+The reference binds graph constants to file tensors by name and checks shape, dtype and
+device on bind (src/io/gguf_weight_loader.cpp:195-240), but silently skips a constant that
+the file lacks (:512-513), which only fails later inside a kernel.  Here the set of names
+must match exactly: one error lists every missing tensor, every unexpected tensor and every
+wrong shape.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import sys
+from typing import Callable, Dict, Iterable, Mapping, Optional
+
+import torch
+
+from ..parts.base import WeightSpec
+from .safetensors_io import SafetensorsFile, open_model_files, write_safetensors
+
+
+class WeightError(ValueError):
+    """The weight file does not fit the model."""
+
+
+def stored_dtype(spec: WeightSpec, file_dtype: torch.dtype, compute: torch.dtype) -> torch.dtype:
+    """The type a tensor is kept in on the device.  32-bit engine: everything is widened to
+    float32.  bfloat16 engine: matrices are bfloat16 (a 32-bit file matrix is rounded to nearest
+    even); vectors stored in 32-bit stay 32-bit, 16-bit ones stay bfloat16 (float16 is widened);
+    integer tables are int32."""
+    if spec.role == "table":
+        return torch.int32
+    if compute == torch.float32:
+        return torch.float32
+    if spec.role == "matrix":
+        return torch.bfloat16
+    return torch.bfloat16 if file_dtype == torch.bfloat16 else torch.float32
+
+
+def check_names_and_shapes(specs: Mapping[str, WeightSpec], found: Mapping[str, tuple],
+                           ignorable: Iterable[str] = ()) -> None:
+    missing = sorted(n for n in specs if n not in found)
+    unexpected = sorted(n for n in found if n not in specs and n not in set(ignorable))
+    wrong = sorted((n, tuple(found[n]), tuple(specs[n].shape)) for n in specs
+                   if n in found and tuple(found[n]) != tuple(specs[n].shape))
+    if not (missing or unexpected or wrong):
+        return
+    lines = ["the weight file does not fit the model:"]
+    if missing:
+        lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
+    if unexpected:
+        lines.append(f"  unexpected tensors ({len(unexpected)}): " + ", ".join(unexpected))
+    if wrong:
+        lines.append(f"  wrong shapes ({len(wrong)}): " + "; ".join(
+            f"{n} is {list(got)}, expected {list(want)}" for n, got, want in wrong))
+    raise WeightError("\n".join(lines))
+
+
+def load_model_weights(model, config, model_dir: str, compute: torch.dtype, device: torch.device) -> None:
+    """Read every tensor the model declares from the folder's safetensors file(s)."""
+    files = open_model_files(model_dir)
+    canonical = getattr(config, "canonical_tensor_name", lambda n: n)
+    where: Dict[str, tuple] = {}
+    for f in files:
+        for raw in f.names():
+            name = canonical(raw)
+            if name in where:
+                raise WeightError(f"tensor {name!r} appears twice in {model_dir} (as {where[name][1]!r} and {raw!r})")
+            where[name] = (f, raw)
+    specs = model.weight_specs()
+    ignorable = []
+    if getattr(config, "tie_word_embeddings", False) and "lm_head.weight" in where and "lm_head.weight" not in specs:
+        # tied models are sometimes saved with a copy of the table under the head's name
+        print("[llmengine_b200] tie_word_embeddings is set: the file's lm_head.weight is ignored, "
+              "the embedding table is used", file=sys.stderr)
+        ignorable.append("lm_head.weight")
+    check_names_and_shapes(specs, {n: f.shape(raw) for n, (f, raw) in where.items()}, ignorable)
+    tensors: Dict[str, torch.Tensor] = {}
+    for name, spec in specs.items():
+        f, raw = where[name]
+        t = f.tensor(raw)
+        tensors[name] = t.to(device=device, dtype=stored_dtype(spec, t.dtype, compute), copy=True)
+    model.load_weights(tensors)
+
+
+# ----------------------------------------------------------------------------- random weights
+def _tensor_seed(seed: int, name: str) -> int:
+    return int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little") & (2**63 - 1)
+
+
+def random_tensor(name: str, spec: WeightSpec, seed: int, device: torch.device = torch.device("cpu")) -> torch.Tensor:
+    """A tensor drawn from (seed, name) alone, so values do not depend on the order of generation:
+    "normal" ~ N(0, 0.02), "gain" ~ 1 + N(0, 0.1), 32-bit.  (CPU and CUDA generators give
+    different streams; a model folder is always written from the CPU stream.)"""
+    g = torch.Generator(device=device)
+    g.manual_seed(_tensor_seed(seed, name))
+    z = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
+    if spec.init == "gain":
+        return 1.0 + 0.1 * z
+    if spec.init == "normal":
+        return 0.02 * z
+    raise ValueError(f"tensor {name!r}: unknown init {spec.init!r}")
+
+
+def random_model_weights(model, seed: int, compute: torch.dtype, device: torch.device,
+                         file_dtype: torch.dtype = torch.bfloat16) -> None:
+    """Fill a model with random weights directly on the device (no folder is written).
+    Values pass through `file_dtype` as they would through a file."""
+    tensors = {}
+    for name, spec in model.weight_specs().items():
+        t = random_tensor(name, spec, seed, device).to(file_dtype)
+        tensors[name] = t.to(stored_dtype(spec, file_dtype, compute))
+    model.load_weights(tensors)
+
+
+def write_random_model(config, seed: int, out_dir: str, dtype: str = "bfloat16") -> str:
+    """Random-weights mode: write `config.json` and `model.safetensors` for a configuration and a seed."""
+    from ..engine.model import Model
+    from ..parts.base import Runtime
+
+    file_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
+    os.makedirs(out_dir, exist_ok=True)
+    model = Model(config.model_spec(), Runtime(None, torch.device("cpu"), torch.float32, 1))
+    tensors = {n: random_tensor(n, s, seed).to(file_dtype) for n, s in model.weight_specs().items()}
+    d = config.to_dict()
+    d["torch_dtype"] = dtype
+    with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
+        json.dump(d, f, indent=2)
+    write_safetensors(os.path.join(out_dir, "model.safetensors"), tensors,
+                      {"format": "pt", "seed": str(seed)})
+    return out_dir
