@@ -1,0 +1,329 @@
+"""Each CUDA kernel alone against a plain 32-bit reference of the same operation, at sizes other
+than the engine tests use (widths and vocabularies that are no power of two, head sizes in
+steps of 16, several group sizes).  Where random inputs would hide a fault, the inputs are
+made so that it shows: one key that dominates the softmax far back in a long context, at a
+window's edge or on either side of a page's edge."""
+import math
+
+import pytest
+import torch
+
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from llmengine_b200.kernels.ops import CudaOps
+    return CudaOps(torch.device(DEV))
+
+
+def _rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ----------------------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,vocab", [(72, 301), (1000, 77), (4096, 513)])
+def test_embedding(ops, dtype, hidden, vocab):
+    table = _rand(vocab, hidden, dtype=dtype, seed=1)
+    ids = torch.randint(0, vocab, (37,), generator=torch.Generator().manual_seed(2)).to(torch.int32).to(DEV)
+    out = torch.empty(37, hidden, device=DEV)
+    ops.embedding(ids, table, out)
+    want = pm.embedding(table.cpu().float(), ids.cpu().tolist())
+    assert torch.equal(out.cpu(), want)
+
+
+# ----------------------------------------------------------------------------- rmsnorm
+@pytest.mark.parametrize("hidden", [48, 96, 1000, 4096, 5120])
+@pytest.mark.parametrize("gain_dtype,out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                                  (torch.float32, torch.bfloat16)])
+def test_rmsnorm(ops, hidden, gain_dtype, out_dtype):
+    eps = 3e-6
+    x = _rand(19, hidden, seed=3, scale=2.0)
+    gain = (1 + 0.1 * _rand(hidden, seed=4)).to(gain_dtype)
+    out = torch.empty(19, hidden, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, gain, eps, out)
+    want = pm.rms_norm(x.cpu(), gain.cpu().float(), eps)
+    tol = 1e-5 if out_dtype == torch.float32 else 2e-2
+    assert (out.cpu().float() - want).abs().max() < tol
+    if out_dtype == torch.bfloat16:      # rounding is the only difference
+        assert (out.cpu().float() - want.to(torch.bfloat16).float()).abs().max() <= 0.016 * want.abs().max()
+
+
+@pytest.mark.parametrize("delta_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_adds_delta_and_selects_rows(ops, delta_dtype):
+    hidden, eps = 200, 1e-5
+    x = _rand(23, hidden, seed=5)
+    delta = _rand(23, hidden, seed=6).to(delta_dtype)
+    gain = 1 + 0.1 * _rand(hidden, seed=7)
+    x0 = x.clone()
+    out = torch.empty(23, hidden, device=DEV)
+    ops.rmsnorm(x, gain, eps, out, delta=delta)
+    total = x0.cpu() + delta.cpu().float()
+    assert torch.allclose(x.cpu(), total, atol=0, rtol=0), "the sum must be stored back into the residual stream"
+    assert (out.cpu() - pm.rms_norm(total, gain.cpu(), eps)).abs().max() < 1e-5
+    rows = torch.tensor([22, 0, 7], dtype=torch.int32, device=DEV)
+    x2 = x0.clone()
+    out2 = torch.empty(3, hidden, device=DEV)
+    ops.rmsnorm(x2, gain, eps, out2, delta=delta, rows=rows)
+    assert (out2.cpu() - pm.rms_norm(total[[22, 0, 7]], gain.cpu(), eps)).abs().max() < 1e-5
+
+
+# ----------------------------------------------------------------------------- swiglu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter", [56, 1000, 12288])
+def test_swiglu(ops, dtype, inter):
+    gu = _rand(9, 2 * inter, dtype=dtype, seed=8, scale=3.0)
+    out = torch.empty(9, inter, dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    f = gu.cpu().float()
+    want = pm.swiglu(f[:, :inter], f[:, inter:])
+    if dtype == torch.float32:
+        assert (out.cpu() - want).abs().max() < 1e-5
+    else:                                 # one rounding of the result to bfloat16
+        assert ((out.cpu().float() - want).abs() <= want.abs() * 2 ** -8 + 1e-6).all()
+
+
+# ----------------------------------------------------------------------------- 32-bit matrix product
+@pytest.mark.parametrize("M,N,K", [(1, 130, 70), (7, 64, 64), (65, 129, 257), (200, 1000, 96), (33, 48, 4096)])
+def test_gemm_f32_is_true_32bit(ops, M, N, K):
+    a = _rand(M, K, seed=9)
+    w = _rand(N, K, seed=10)
+    out = torch.empty(M, N, device=DEV)
+    ops.linear(a, w, out)
+    want = a.cpu().double() @ w.cpu().double().t()
+    err = (out.cpu().double() - want).abs().max().item()
+    # a product in a reduced-precision mode would be off by ~1e-3 * sqrt(K); true 32-bit stays near 1e-6 * sqrt(K)
+    assert err < 2e-6 * math.sqrt(K) * 4, err
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch(ops):
+    a = _rand(100, 300, seed=11)
+    w = _rand(77, 300, seed=12)
+    full = torch.empty(100, 77, device=DEV)
+    ops.linear(a, w, full)
+    one = torch.empty(1, 77, device=DEV)
+    for r in (0, 63, 64, 99):
+        ops.linear(a[r:r + 1].contiguous(), w, one)
+        assert torch.equal(one[0], full[r])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (8, 1000, 96), (130, 520, 264)])
+def test_linear_bf16(ops, M, N, K):
+    a = _rand(M, K, dtype=torch.bfloat16, seed=13)
+    w = _rand(N, K, dtype=torch.bfloat16, seed=14)
+    want = a.cpu().float() @ w.cpu().float().t()
+    out32 = torch.empty(M, N, device=DEV)
+    ops.linear(a, w, out32)
+    assert (out32.cpu() - want).abs().max() < 1e-3 * math.sqrt(K)
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear(a, w, out16)
+    assert (out16.cpu().float() - want).abs().max() < 0.02 * want.abs().max()
+
+
+# ----------------------------------------------------------------------------- QK norm + rope + cache write
+def _paged_layout(T, page_size, num_pages, seed):
+    """Scatter T consecutive positions over pages in a scrambled order."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = torch.randperm(num_pages, generator=g)[: -(-T // page_size)]
+    pos = torch.arange(T)
+    slots = blocks[pos // page_size] * page_size + pos % page_size
+    return blocks.to(torch.int32), slots.to(torch.int32)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 8), (6, 3, 48, 16), (8, 1, 80, 4), (32, 8, 128, 16), (2, 2, 256, 32)])
+def test_qkv_post(ops, dtype, nh, nkv, hd, page):
+    from llmengine_b200.parts.position import RotaryEncoding
+    T, eps, theta, maxpos = 29, 2e-6, 12345.0, 300
+    qs, kvs = nh * hd, nkv * hd
+    qkv = _rand(T, qs + 2 * kvs, dtype=dtype, seed=15)
+    qg = (1 + 0.1 * _rand(hd, seed=16))
+    kg = (1 + 0.1 * _rand(hd, seed=17))
+    table = RotaryEncoding.build_table(hd, theta, maxpos).to(DEV)
+    positions = (torch.arange(T) + 200).to(torch.int32).to(DEV)
+    num_pages = 12
+    blocks, slots = _paged_layout(T, page, num_pages, 18)
+    slots[5] = -1                                     # a token that is not stored
+    cache = torch.zeros(num_pages, 2, nkv, page, hd, dtype=dtype, device=DEV)
+    q_out = torch.empty(T, qs, dtype=dtype, device=DEV)
+    ops.qkv_post(q_in=qkv[:, :qs], k_in=qkv[:, qs:qs + kvs], v_in=qkv[:, qs + kvs:], num_heads=nh, num_kv_heads=nkv,
+                 head_dim=hd, q_gain=qg, k_gain=kg, eps=eps, cos_sin=table, positions=positions, q_out=q_out,
+                 cache=cache, slot_mapping=slots.to(DEV), page_size=page)
+    f = qkv.cpu().float()
+    pos = positions.cpu()
+    q_want = pm.rope(pm.qk_norm(f[:, :qs].view(T, nh, hd), qg.cpu(), eps), pos, theta).reshape(T, qs)
+    k_want = pm.rope(pm.qk_norm(f[:, qs:qs + kvs].view(T, nkv, hd), kg.cpu(), eps), pos, theta)
+    v_want = f[:, qs + kvs:].view(T, nkv, hd)
+    tol = 2e-5 if dtype == torch.float32 else 0.04
+    assert (q_out.cpu().float() - q_want).abs().max() < tol
+    c = cache.cpu().float()
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        assert (c[s // page, 0, :, s % page] - k_want[t]).abs().max() < tol
+        assert (c[s // page, 1, :, s % page] - v_want[t]).abs().max() < tol
+    written = {int(s) for s in slots if s >= 0}
+    for s in range(num_pages * page):
+        if s not in written:
+            assert c[s // page, :, :, s % page].abs().max() == 0, "a cache row that no token maps to was written"
+
+
+# ----------------------------------------------------------------------------- attention
+def _attention_case(nh, nkv, hd, page, ctx_lens, q_lens, window, dtype, seed, spike=None):
+    """Builds a paged cache holding `ctx_lens[r]` keys per request and queries for the last
+    `q_lens[r]` positions of each.  Returns kernel inputs and the plain result.
+    `spike = (request, key position)`: that key is aligned with the request's last query and
+    scaled so that it takes nearly all of the softmax weight."""
+    R = len(ctx_lens)
+    g = torch.Generator().manual_seed(seed)
+    num_pages = sum(-(-c // page) for c in ctx_lens) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    max_blocks = max(-(-c // page) for c in ctx_lens) + 1
+    tables = torch.full((R + 2, max_blocks), -1, dtype=torch.int32)
+    cache = torch.full((num_pages, 2, nkv, page, hd), float("nan"))       # unwritten rows stay NaN
+    ks, vs, qs = [], [], []
+    for r, c in enumerate(ctx_lens):
+        k = torch.randn(c, nkv, hd, generator=g)
+        v = torch.randn(c, nkv, hd, generator=g)
+        q = torch.randn(c, nh, hd, generator=g)
+        if spike is not None and spike[0] == r:
+            j = spike[1]
+            grp = nh // nkv
+            for kvh in range(nkv):          # score of key j becomes ~2*sqrt(hd) for every query head, others ~N(0,1)
+                k[j, kvh] = 2.0 * q[c - 1, kvh * grp:(kvh + 1) * grp].sum(0)
+        ks.append(k), vs.append(v), qs.append(q)
+        row = r + 1                                                        # table rows need not be 0..R-1
+        for b in range(-(-c // page)):
+            p = perm.pop()
+            tables[row, b] = p
+            n = min(page, c - b * page)
+            cache[p, 0, :, :n] = k[b * page:b * page + n].transpose(0, 1)
+            cache[p, 1, :, :n] = v[b * page:b * page + n].transpose(0, 1)
+    cache = cache.to(dtype)
+    q_rows, positions, token_req, want = [], [], [], []
+    for r, (c, n) in enumerate(zip(ctx_lens, q_lens)):
+        kf = cache_round(ks[r], dtype)
+        vf = cache_round(vs[r], dtype)
+        qf = cache_round(qs[r], dtype)
+        full = pm.attention(qf, kf, vf, window)
+        for p in range(c - n, c):
+            q_rows.append(qf[p].reshape(-1))
+            positions.append(p)
+            token_req.append(r + 1)
+            want.append(full[p].reshape(-1))
+    return dict(
+        q=torch.stack(q_rows).to(dtype).to(DEV), cache=cache.to(DEV),
+        positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+        token_request=torch.tensor(token_req, dtype=torch.int32, device=DEV),
+        block_tables=tables.to(DEV), want=torch.stack(want))
+
+
+def cache_round(x, dtype):
+    return x.to(dtype).float()
+
+
+ATTN_SHAPES = [(4, 2, 16, 8), (6, 3, 48, 16), (8, 1, 80, 4), (8, 2, 128, 16), (3, 3, 32, 16), (16, 4, 64, 32)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,page", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [0, 13])
+def test_attention_plain_mixed_batch(ops, dtype, nh, nkv, hd, page, window):
+    case = _attention_case(nh, nkv, hd, page, ctx_lens=[1, 37, 64, 150], q_lens=[1, 37, 1, 9], window=window,
+                           dtype=dtype, seed=20)
+    out = torch.empty_like(case["q"])
+    ops.attention_plain(q=case["q"], cache=case["cache"], out=out, positions=case["positions"],
+                        token_request=case["token_request"], block_tables=case["block_tables"], num_heads=nh,
+                        num_kv_heads=nkv, head_dim=hd, page_size=page, window=window, scale=1 / math.sqrt(hd))
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert torch.isfinite(out).all()
+    assert (out.cpu().float() - case["want"]).abs().max() < tol
+
+
+@pytest.mark.parametrize("where", ["far_back", "page_last", "page_first", "window_inside", "window_outside"])
+def test_attention_plain_finds_the_one_key_that_matters(ops, where):
+    nh, nkv, hd, page, ctx, window = 8, 2, 64, 16, 700, 0
+    key = {"far_back": 3, "page_last": 16 * 20 - 1, "page_first": 16 * 20}.get(where)
+    if where.startswith("window"):
+        window = 100
+        key = ctx - 100 if where == "window_inside" else ctx - 101       # query at ctx-1 sees keys > ctx-1-100
+    case = _attention_case(nh, nkv, hd, page, [ctx], [1], window, torch.float32, 21, spike=(0, key))
+    out = torch.empty_like(case["q"])
+    ops.attention_plain(q=case["q"], cache=case["cache"], out=out, positions=case["positions"],
+                        token_request=case["token_request"], block_tables=case["block_tables"], num_heads=nh,
+                        num_kv_heads=nkv, head_dim=hd, page_size=page, window=window, scale=1 / math.sqrt(hd))
+    assert (out.cpu() - case["want"]).abs().max() < 2e-5
+
+
+# ----------------------------------------------------------------------------- sampling
+def _sample(ops, logits, **kw):
+    R = logits.shape[0]
+    dev = lambda v, dt: torch.tensor(v, dtype=dt, device=DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits, greedy=dev(kw["greedy"], torch.int32), temperature=dev(kw["temperature"], torch.float32),
+               top_k=dev(kw["top_k"], torch.int32), top_p=dev(kw["top_p"], torch.float32),
+               u=dev(kw["u"], torch.float32), out=out)
+    return out.cpu().tolist()
+
+
+@pytest.mark.parametrize("vocab", [77, 1000, 151936])
+def test_sample_greedy_is_first_argmax(ops, vocab):
+    logits = _rand(5, vocab, seed=22)
+    logits[1, 10] = logits[1, 40] = 50.0           # a tie: the first one wins
+    logits[2] = float("-inf")                      # src/runtime/sampler.cpp:41-47: uniform, token 0
+    got = _sample(ops, logits, greedy=[1] * 5, temperature=[1.0, 0.5, 1.0, 0.0, 2.0], top_k=[0] * 5, top_p=[0.0] * 5,
+                  u=[0.5] * 5)
+    want = [int(torch.argmax(logits[i].cpu())) for i in range(5)]
+    want[1], want[2] = 10, 0
+    assert got == want
+
+
+@pytest.mark.parametrize("vocab", [77, 5000])
+def test_sample_draw_follows_the_cdf(ops, vocab):
+    logits = _rand(1, vocab, seed=23, scale=2.0)
+    for temperature, top_k, top_p in [(1.0, 0, 0.0), (0.7, 0, 0.0), (1.3, 12, 0.0), (1.0, 0, 0.8), (0.9, 20, 0.6)]:
+        for u in (0.003, 0.21, 0.5, 0.77, 0.999):
+            got = _sample(ops, logits, greedy=[0], temperature=[temperature], top_k=[top_k], top_p=[top_p], u=[u])[0]
+            want = pm.plain_sample(logits[0].cpu(), greedy=False, temperature=temperature, top_k=top_k, top_p=top_p, u=u)
+            if got != want:
+                # sums in another order may move a boundary by a rounding step: then u must lie on it
+                z = logits[0].cpu().double() / temperature
+                p = torch.softmax(z, 0)
+                lo, hi = sorted((got, want))
+                kept = _kept(p, top_k, top_p)
+                cdf = torch.cumsum(torch.where(kept, p, torch.zeros((), dtype=torch.double)), 0) / p[kept].sum()
+                assert kept[got], (temperature, top_k, top_p, u)
+                assert abs(float(cdf[lo]) - u) < 1e-4 and not kept[lo + 1:hi].any(), (temperature, top_k, top_p, u, got, want)
+
+
+def _kept(p, top_k, top_p):
+    keep = torch.ones_like(p, dtype=torch.bool)
+    if 0 < top_k < p.numel():
+        keep &= p >= torch.sort(p, descending=True).values[top_k - 1]
+    if 0 < top_p < 1:
+        sp = torch.sort(torch.where(keep, p, torch.zeros((), dtype=p.dtype)), descending=True).values
+        cut = int((torch.cumsum(sp, 0) >= top_p).nonzero()[0])
+        keep &= p >= sp[cut]
+    return keep
+
+
+def test_repetition_penalty(ops):
+    logits = _rand(3, 50, seed=24)
+    ref = logits.cpu().clone()
+    rows = torch.tensor([0, 0, 2], dtype=torch.int32, device=DEV)
+    toks = torch.tensor([4, 9, 9], dtype=torch.int32, device=DEV)
+    counts = torch.tensor([1, 3, 2], dtype=torch.int32, device=DEV)
+    pen = torch.tensor([1.1, 1.0, 1.5], device=DEV)
+    ops.repetition_penalty(logits, rows, toks, counts, pen)
+    for r, t, c in ((0, 4, 1), (0, 9, 3), (2, 9, 2)):
+        v = ref[r, t]
+        for _ in range(c):
+            v = v / pen[r].item() if v > 0 else v * pen[r].item()
+        ref[r, t] = v
+    assert torch.allclose(logits.cpu(), ref, atol=1e-6)

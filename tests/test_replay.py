@@ -1,0 +1,107 @@
+"""Replay of the same requests under different ways of cutting them into steps, compared with
+the plain implementation: whole; most of it in one step and the last 32 tokens one by one; in
+portions of changing size down to two tokens; mixed, up to four live requests with so few
+pages that they are used again.  In 32-bit and in bfloat16 on the GPU; the host logic alone
+(batch metadata, cache bookkeeping) also runs without a GPU against a CPU stand-in for the
+kernels."""
+import os
+import subprocess
+import sys
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (compare, engine_for, make_model_dir, max_live_tokens, random_ids, replay, trace_bulk_then_single,
+                     trace_mixed, trace_portions, trace_whole)
+from plain_model import PlainQwen3
+from tiny_configs import TINY_A, TINY_B, TINY_C
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# Largest |logit difference| allowed against the plain implementation.  Logits of these models
+# are of order 1.  32-bit: sums in another order.  bfloat16: the plain implementation rounds
+# at the same places, what remains is the order of sums and values that fall on the other side
+# of a rounding step.
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+
+CONFIGS = {
+    "A": (TINY_A, 16, [70, 33, 100, 19, 45, 64, 7]),
+    "B": (TINY_B, 8, [1, 5, 64, 130, 200, 48]),
+    "C": (TINY_C, 16, [90, 37, 120, 64, 23]),
+}
+
+
+def _setup(tmp_path, name, dtype, sharpen):
+    cfg, page, lens = CONFIGS[name]
+    d = make_model_dir(str(tmp_path / f"{name}_{dtype}"), cfg, seed=11, dtype="bfloat16", sharpen=sharpen)
+    reqs = {f"r{i}": random_ids(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(lens)}
+    plain = PlainQwen3(d, round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    ref = {r: plain.logits(ids) for r, ids in reqs.items()}
+    return d, page, reqs, ref
+
+
+def _traces(reqs):
+    prompt = {r: max(1, len(ids) - 12) for r, ids in reqs.items()}
+    return {
+        "whole": trace_whole(reqs),
+        "bulk_then_single": trace_bulk_then_single(reqs, 32),
+        "portions": trace_portions(reqs),
+        "mixed": trace_mixed(reqs, prompt, max_live=4, seed=3),
+    }
+
+
+def _run_all(tmp_path, name, dtype, sharpen, ops, device):
+    d, page, reqs, ref = _setup(tmp_path, name, dtype, sharpen)
+    worst = {}
+    for what, steps in _traces(reqs).items():
+        pool = max_live_tokens(steps, 64)
+        eng = engine_for(d, dtype, pool, page_size=page, ops=ops, device=device)
+        got = replay(eng, steps, poison=True)
+        worst[what] = compare(got, ref, TOL[dtype], f"{name}/{dtype}/{what}")
+        eng.cache.check_invariants()
+        assert not eng.cache.requests, "every request was ended, nothing may be held"
+        assert all(g.pool.free_count == g.pool.num_pages for g in eng.cache.groups)
+    return worst
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_host_logic_replay_cpu(tmp_path, name):
+    from host_ops import HostOps
+    _run_all(tmp_path, name, "float32", 1.0, HostOps(), "cpu")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sharpen", [1.0, 3.0])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_gpu(tmp_path, name, dtype, sharpen):
+    worst = _run_all(tmp_path, name, dtype, sharpen, None, "cuda:0")
+    print(f"replay {name} {dtype} sharpen={sharpen}: " + ", ".join(f"{k} {v:.2e}" for k, v in worst.items()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """The program itself, as a user calls it: JSON lines in, <step>.f32 files and `done` lines out."""
+    d, page, reqs, ref = _setup(tmp_path, "B", dtype, 2.0)
+    steps = _traces(reqs)["mixed"]
+    out = tmp_path / "out"
+    lines = [json.dumps({"step": i, "entries": [{"id": r, "tokens": t, "want": w} for r, t, w in e], "end": end})
+             for i, (e, end) in enumerate(steps)]
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", str(max_live_tokens(steps, 64))],
+                       input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+    rows = {}
+    V = TINY_B["vocab_size"]
+    for i, (e, _) in enumerate(steps):
+        arr = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V))
+        k = 0
+        for r, t, w in e:
+            rows.setdefault(r, []).append(arr[k:k + len(w)])
+            k += len(w)
+        assert k == arr.shape[0]
+    compare({r: torch.cat(v) for r, v in rows.items()}, ref, TOL[dtype], f"trace_run/{dtype}")
