@@ -6,5 +6,17 @@ parts, a paged cache with block tables, one step function for mixed batches, a s
 samplers, and hand-written CUDA kernels.
 """
 from .config import EngineConfig, load_config  # noqa: F401
+from .sampling import SamplingParams  # noqa: F401
+
+
+def __getattr__(name):
+    # the engine classes import torch-heavy modules: resolve them on first use
+    if name in ("LLM", "GenerationOutput"):
+        from .engine import llm
+        return getattr(llm, name)
+    if name in ("Engine", "StepEntry", "StepError"):
+        from .engine import engine
+        return getattr(engine, name)
+    raise AttributeError(name)
 
 __version__ = "0.1.0"

@@ -1,0 +1,540 @@
+// Paged attention on the tensor cores for bfloat16 queries and caches, compiled for one head
+// size (HEAD_DIM, a multiple of 16 up to 128, given on the nvcc command line).
+//
+//   attention_portion_kernel  prompt portions of any length at any start position: a tile of 64
+//                             (token, query-head-of-the-group) rows per block, flash-attention
+//                             style: keys and values stream through shared memory in tiles of 64,
+//                             scores and the running softmax stay in registers, 32-bit.
+//   attention_decode_kernel   one new token per request: the query heads of one key/value head
+//                             form the (padded) 16-row tile, the context is split over blocks and
+//                             over the four warps of a block, partial (max, sum, output) triples go
+//                             to scratch memory and attention_combine_kernel merges them.
+//
+// Both read keys and values only from the cache pages through the block table, mask by the
+// absolute position of each query (causal, optional window) and never let a cache row outside
+// the needed range reach the arithmetic: such rows are replaced by zeros while loading, so
+// stale or never-written memory (NaN included) cannot leak into a result.
+//
+// Reference counterparts: flash_sdpa_tiled_kernel (src/runtime/kernels/cuda_kernels.cu:558-645,
+// one block per query row, scalar FMA) and paged_attention_decode_batch_kernel (:697-754, one
+// block per head walking the keys one at a time).
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<multiple of 16, at most 128>"
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "HEAD_DIM must be a multiple of 16 in 16..128");
+
+LLME_API const char* llme_last_error() { return llme_error_buffer(); }
+
+namespace {
+
+constexpr int HD = HEAD_DIM;
+constexpr int BM = 64;            // rows of a portion tile (4 warps x 16)
+constexpr int BN = 64;            // keys per shared-memory tile
+constexpr int LDS = HD + 8;       // padded row length in shared memory (elements): conflict-free ldmatrix
+constexpr int THREADS = 128;
+constexpr int KSTEPS = HD / 16;   // k-steps of Q K^T
+constexpr int DTILES = HD / 8;    // n-tiles of P V
+constexpr float LOG2E = 1.4426950408889634f;
+
+typedef __nv_bfloat16 bf16;
+
+struct FastAttnArgs {
+    const bf16* q;               // [T, nh, HD]
+    const bf16* cache;           // [pages][K|V][nkv][page_size][HD]
+    bf16* out;                   // [T, nh, HD]
+    const int* rows;             // [n_rows] batch rows (requests) this launch serves
+    const int* cu_q_lens;        // [R+1]
+    const int* ctx_lens;         // [R] cached length after this step
+    const int* table_rows;       // [R] row of block_tables of each request
+    const int* block_tables;     // [*, max_blocks]
+    float* scratch;              // decode partials
+    int max_blocks, n_rows, nh, nkv, page_size, window, splits;
+    float scale;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+// 16-byte asynchronous copy; with valid == false the destination is filled with zeros.
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+// D += A(16x16, row) * B(16x8, col), bfloat16 operands, 32-bit accumulators
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Load keys [j0, j0+BN) of one key/value head into a [BN][LDS] shared tile (K or V).  Keys outside
+// [lo, hi] become zeros.
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* cache, const int* bt, int which, int kvh, int nkv,
+                                             int ps, int j0, int lo, int hi) {
+    constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per key row
+    for (int c = threadIdx.x; c < BN * CHUNKS; c += THREADS) {
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        const int j = j0 + r;
+        const bool valid = j >= lo && j <= hi;
+        const bf16* src = cache;
+        if (valid) {
+            const int blk = j / ps;
+            const int page = bt[blk];
+            src = cache + ((((size_t)page * 2 + which) * nkv + kvh) * ps + (j - blk * ps)) * HD + ch * 8;
+        }
+        cp_async_16(dst + r * LDS + ch * 8, src, valid);
+    }
+}
+
+// One warp: scores of its 16 rows against NT*8 keys starting at shared row `key0` of the K tile.
+template <int NT>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const unsigned (&qf)[KSTEPS][4], const bf16* Ks, int key0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+            unsigned b[4];
+            const int mi = lane >> 3;
+            ldmatrix_x4(b, Ks + (key0 + np * 16 + (lane & 7) + (mi >> 1) * 8) * LDS + kk * 16 + (mi & 1) * 8);
+            mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
+            mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+        }
+    }
+}
+
+// One warp: o += P V for NT*8 keys starting at shared row `key0` of the V tile; p holds the
+// probabilities in the accumulator layout of the scores.
+template <int NT>
+__device__ __forceinline__ void pv_tile(float (&o)[DTILES][4], const float (&p)[NT][4], const bf16* Vs, int key0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        unsigned a[4];
+        a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+        a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+        a[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+        a[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+            unsigned b[4];
+            const int mi = lane >> 3;
+            ldmatrix_x4_trans(b, Vs + (key0 + kk * 16 + (lane & 7) + (mi & 1) * 8) * LDS + dp * 16 + (mi >> 1) * 8);
+            mma_bf16(o[2 * dp], a, b[0], b[1]);
+            mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// Mask, running maximum and sum for the two rows a thread holds (r0 = lane/4, r1 = r0 + 8).
+// s is scaled to base-2 exponent units on entry and holds the probabilities on exit.
+// key index of s[n][c] is jbase + n*8 + (lane%4)*2 + (c&1); rows c<2 -> r0, c>=2 -> r1.
+template <int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[DTILES][4],
+                                               int jbase, const int (&plo)[2], const int (&phi)[2]) {
+    const int lane = threadIdx.x & 31;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int j = jbase + n * 8 + (lane & 3) * 2 + (c & 1);
+            const int r = c >> 1;
+            if (j < plo[r] || j > phi[r]) s[n][c] = -INFINITY;
+            mx[r] = fmaxf(mx[r], s[n][c]);
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    float corr[2], mnew[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mnew[r] = fmaxf(m[r], mx[r]);
+        // a row that has seen no key yet keeps m = -inf: use 0 as the reference point so that exp2 gives 0, not NaN
+        const float ref = mnew[r] == -INFINITY ? 0.0f : mnew[r];
+        corr[r] = exp2f(m[r] - ref);
+        m[r] = mnew[r];
+        mnew[r] = ref;
+    }
+    float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float e = exp2f(s[n][c] - mnew[c >> 1]);
+            s[n][c] = e;
+            sum[c >> 1] += e;
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        l[r] = l[r] * corr[r] + sum[r];
+    }
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[0];
+        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+    }
+}
+
+// ----------------------------------------------------------------------------- portions
+__global__ void __launch_bounds__(THREADS) attention_portion_kernel(FastAttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS]
+    bf16* Ks = Qs + BM * LDS;                              // [2][BN][LDS]
+    bf16* Vs = Ks + 2 * BN * LDS;                          // [2][BN][LDS]
+
+    const int r = a.rows[blockIdx.z];
+    const int kvh = blockIdx.y;
+    const int G = a.nh / a.nkv;
+    const int q0 = a.cu_q_lens[r];
+    const int q_len = a.cu_q_lens[r + 1] - q0;
+    const int M = q_len * G;
+    const int m0 = blockIdx.x * BM;
+    if (m0 >= M) return;
+    const int start = a.ctx_lens[r] - q_len;               // position of the portion's first token
+    const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // rows of the tile -> (token, head of the group)
+    const int t_lo = m0 / G;
+    const int t_hi = min(q_len - 1, (m0 + BM - 1) / G);
+    const int hi_max = start + t_hi;
+    const int lo_min = a.window > 0 ? max(0, start + t_lo - a.window + 1) : 0;
+
+    // Q tile
+    {
+        constexpr int CHUNKS = HD / 8;
+        for (int c = threadIdx.x; c < BM * CHUNKS; c += THREADS) {
+            const int row = c / CHUNKS, ch = c - row * CHUNKS;
+            const int m = m0 + row;
+            const bool valid = m < M;
+            const bf16* src = a.q;
+            if (valid) src = a.q + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD + ch * 8;
+            cp_async_16(Qs + row * LDS + ch * 8, src, valid);
+        }
+    }
+    const int j_first = (lo_min / BN) * BN;
+    load_kv_tile(Ks, a.cache, bt, 0, kvh, a.nkv, a.page_size, j_first, lo_min, hi_max);
+    load_kv_tile(Vs, a.cache, bt, 1, kvh, a.nkv, a.page_size, j_first, lo_min, hi_max);
+    cp_async_commit();
+
+    // this thread's two rows
+    int plo[2], phi[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = m0 + warp * 16 + (lane >> 2) + i * 8;
+        const int p = start + min(m, M - 1) / G;
+        phi[i] = m < M ? p : -1;                            // rows past the portion see no key
+        plo[i] = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[DTILES][4];
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
+    unsigned qf[KSTEPS][4];
+    const float sc = a.scale * LOG2E;
+
+    int buf = 0;
+    for (int j0 = j_first; j0 <= hi_max; j0 += BN) {
+        const int jn = j0 + BN;
+        if (jn <= hi_max) {
+            load_kv_tile(Ks + (buf ^ 1) * BN * LDS, a.cache, bt, 0, kvh, a.nkv, a.page_size, jn, lo_min, hi_max);
+            load_kv_tile(Vs + (buf ^ 1) * BN * LDS, a.cache, bt, 1, kvh, a.nkv, a.page_size, jn, lo_min, hi_max);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (j0 == j_first) {
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk)
+                ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 16 + (lane >> 4) * 8);
+        }
+        const bf16* Kt = Ks + buf * BN * LDS;
+        const bf16* Vt = Vs + buf * BN * LDS;
+        // the warp's rows see keys up to the larger of its two thread-row limits; whole-tile skip when none
+        const int warp_hi = start + min(q_len - 1, (m0 + warp * 16 + 15) / G);
+        if (j0 <= warp_hi && m0 + warp * 16 < M) {
+            float s[BN / 8][4];
+            qk_tile<BN / 8>(s, qf, Kt, 0);
+#pragma unroll
+            for (int n = 0; n < BN / 8; ++n)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) s[n][c] *= sc;
+            softmax_update<BN / 8>(s, m_run, l_run, o, j0, plo, phi);
+            pv_tile<BN / 8>(o, s, Vt, 0);
+        }
+        __syncthreads();
+        buf ^= 1;
+    }
+    cp_async_wait<0>();
+
+    // write the rows
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = m0 + warp * 16 + (lane >> 2) + i * 8;
+        if (m >= M) continue;
+        const float inv = 1.0f / l_run[i];
+        bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+            const int col = d * 8 + (lane & 3) * 2;
+            *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------- decode
+// grid (splits, nkv * head_chunks, n_rows).  Scratch per (request row, query head, split): HD outputs
+// (not normalised), then max (base-2 units) and sum.
+constexpr int PART = HD + 2;
+
+__global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][LDS]
+    bf16* Ks = Qs + 16 * LDS;                              // [2][BN][LDS]
+    bf16* Vs = Ks + 2 * BN * LDS;                          // [2][BN][LDS]
+    float* red = reinterpret_cast<float*>(Ks);              // [4 warps][16 rows][PART], reuses the key tiles after the loop
+
+    const int zi = blockIdx.z;
+    const int r = a.rows[zi];
+    const int G = a.nh / a.nkv;
+    const int chunks = (G + 15) / 16;
+    const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * 16;
+    const int rows_here = min(16, G - g0);
+    const int split = blockIdx.x;
+    const int t = a.cu_q_lens[r];                          // the request's single token
+    const int p = a.ctx_lens[r] - 1;                       // its position
+    const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // this block's share of the key tiles
+    const int tile_first = lo / BN, tile_last = p / BN;
+    const int n_tiles = tile_last - tile_first + 1;
+    const int per = (n_tiles + a.splits - 1) / a.splits;
+    const int my_first = tile_first + split * per;
+    const int my_last = min(tile_last, my_first + per - 1);
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[DTILES][4];
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
+
+    if (my_first <= my_last) {
+        {
+            constexpr int CHUNKS = HD / 8;
+            for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
+                const int row = c / CHUNKS, ch = c - row * CHUNKS;
+                const bool valid = row < rows_here;
+                const bf16* src = a.q;
+                if (valid) src = a.q + ((size_t)t * a.nh + kvh * G + g0 + row) * HD + ch * 8;
+                cp_async_16(Qs + row * LDS + ch * 8, src, valid);
+            }
+        }
+        load_kv_tile(Ks, a.cache, bt, 0, kvh, a.nkv, a.page_size, my_first * BN, lo, p);
+        load_kv_tile(Vs, a.cache, bt, 1, kvh, a.nkv, a.page_size, my_first * BN, lo, p);
+        cp_async_commit();
+        int plo[2] = {lo, lo}, phi[2];
+        phi[0] = (lane >> 2) < rows_here ? p : -1;
+        phi[1] = (lane >> 2) + 8 < rows_here ? p : -1;
+        unsigned qf[KSTEPS][4];
+        const float sc = a.scale * LOG2E;
+        int buf = 0;
+        for (int tile = my_first; tile <= my_last; ++tile) {
+            if (tile + 1 <= my_last) {
+                load_kv_tile(Ks + (buf ^ 1) * BN * LDS, a.cache, bt, 0, kvh, a.nkv, a.page_size, (tile + 1) * BN, lo, p);
+                load_kv_tile(Vs + (buf ^ 1) * BN * LDS, a.cache, bt, 1, kvh, a.nkv, a.page_size, (tile + 1) * BN, lo, p);
+            }
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
+            if (tile == my_first) {
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk)
+                    ldmatrix_x4(qf[kk], Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 16 + (lane >> 4) * 8);
+            }
+            // each warp takes 16 of the tile's 64 keys
+            const int key0 = warp * 16;
+            const int jbase = tile * BN + key0;
+            if (jbase <= p && jbase + 15 >= lo) {
+                float s[2][4];
+                qk_tile<2>(s, qf, Ks + buf * BN * LDS, key0);
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) s[n][c] *= sc;
+                softmax_update<2>(s, m_run, l_run, o, jbase, plo, phi);
+                pv_tile<2>(o, s, Vs + buf * BN * LDS, key0);
+            }
+            __syncthreads();
+            buf ^= 1;
+        }
+        cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    // merge the four warps' partial results in shared memory, in a fixed order
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = (lane >> 2) + i * 8;
+        float* dst = red + ((size_t)warp * 16 + row) * PART;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+            const int col = d * 8 + (lane & 3) * 2;
+            dst[col] = o[d][2 * i];
+            dst[col + 1] = o[d][2 * i + 1];
+        }
+        if ((lane & 3) == 0) {
+            dst[HD] = m_run[i];
+            dst[HD + 1] = l_run[i];
+        }
+    }
+    __syncthreads();
+    for (int row = warp; row < rows_here; row += 4) {
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[((size_t)w * 16 + row) * PART + HD]);
+        const float ref = mm == -INFINITY ? 0.0f : mm;
+        float wgt[4], ll = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            wgt[w] = exp2f(red[((size_t)w * 16 + row) * PART + HD] - ref);
+            ll += wgt[w] * red[((size_t)w * 16 + row) * PART + HD + 1];
+        }
+        const int head = kvh * G + g0 + row;
+        if (a.splits == 1) {
+            bf16* dst = a.out + ((size_t)t * a.nh + head) * HD;
+            const float inv = 1.0f / ll;
+            for (int d = lane; d < HD; d += 32) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + row) * PART + d];
+                dst[d] = __float2bfloat16_rn(acc * inv);
+            }
+        } else {
+            float* dst = a.scratch + (((size_t)zi * a.nh + head) * a.splits + split) * PART;
+            for (int d = lane; d < HD; d += 32) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + row) * PART + d];
+                dst[d] = acc;
+            }
+            if (lane == 0) {
+                dst[HD] = mm;
+                dst[HD + 1] = ll;
+            }
+        }
+    }
+}
+
+// One warp per (request row, query head): merge the splits' partial results.
+__global__ void attention_combine_kernel(FastAttnArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int idx = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (idx >= a.n_rows * a.nh) return;
+    const int zi = idx / a.nh, head = idx - zi * a.nh;
+    const int r = a.rows[zi];
+    const int t = a.cu_q_lens[r];
+    const float* src = a.scratch + (size_t)idx * a.splits * PART;
+    float mm = -INFINITY;
+    for (int s = 0; s < a.splits; ++s) mm = fmaxf(mm, src[s * PART + HD]);
+    const float ref = mm == -INFINITY ? 0.0f : mm;
+    float ll = 0.0f;
+    for (int s = 0; s < a.splits; ++s) ll += exp2f(src[s * PART + HD] - ref) * src[s * PART + HD + 1];
+    const float inv = 1.0f / ll;
+    bf16* dst = a.out + ((size_t)t * a.nh + head) * HD;
+    for (int d = lane; d < HD; d += 32) {
+        float acc = 0.0f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float w = exp2f(src[s * PART + HD] - ref);
+            if (w != 0.0f) acc += w * src[s * PART + d];     // an empty split holds zeros and weight 0
+        }
+        dst[d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+constexpr size_t PORTION_SMEM = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
+constexpr size_t DECODE_SMEM = (size_t)(16 + 4 * BN) * LDS * sizeof(bf16);
+static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)2 * BN * LDS * sizeof(bf16), "the merge buffer must fit the key tiles");
+
+int check_common(const FastAttnArgs& a) {
+    if (!a.q || !a.cache || !a.out || !a.rows || !a.cu_q_lens || !a.ctx_lens || !a.table_rows || !a.block_tables)
+        LLME_REFUSE("attention: null pointer");
+    if (a.nh <= 0 || a.nkv <= 0 || a.nh % a.nkv) LLME_REFUSE("attention: %d query heads are not a multiple of %d key/value heads", a.nh, a.nkv);
+    if (a.page_size <= 0 || a.max_blocks <= 0) LLME_REFUSE("attention: non-positive size");
+    if (a.n_rows > 65535) LLME_REFUSE("attention: more than 65535 requests in one launch");
+    return 0;
+}
+
+}  // namespace
+
+LLME_API int llme_attention_head_dim() { return HD; }
+
+// Floats of scratch that the decode kernel needs for `n_rows` requests.
+LLME_API long long llme_attention_decode_scratch_floats(int n_rows, int nh, int splits) {
+    return splits <= 1 ? 0 : (long long)n_rows * nh * splits * PART;
+}
+
+LLME_API int llme_attention_portion(const FastAttnArgs* args, int max_q_len, cudaStream_t stream) {
+    const FastAttnArgs& a = *args;
+    if (a.n_rows <= 0 || max_q_len <= 0) return 0;
+    if (int rc = check_common(a)) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_portion_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PORTION_SMEM);
+        if (e != cudaSuccess) LLME_REFUSE("attention: cannot reserve %zu bytes of shared memory: %s", PORTION_SMEM, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int G = a.nh / a.nkv;
+    const long long tiles = ((long long)max_q_len * G + BM - 1) / BM;
+    if (tiles > 2147483647LL || a.nkv > 65535) LLME_REFUSE("attention: grid too large");
+    dim3 grid((unsigned)tiles, a.nkv, a.n_rows);
+    attention_portion_kernel<<<grid, THREADS, PORTION_SMEM, stream>>>(a);
+    LLME_LAUNCH_STATUS();
+}
+
+LLME_API int llme_attention_decode(const FastAttnArgs* args, cudaStream_t stream) {
+    const FastAttnArgs& a = *args;
+    if (a.n_rows <= 0) return 0;
+    if (int rc = check_common(a)) return rc;
+    if (a.splits < 1 || a.splits > 1024) LLME_REFUSE("attention: splits must be in 1..1024, got %d", a.splits);
+    if (a.splits > 1 && !a.scratch) LLME_REFUSE("attention: split decoding needs scratch memory");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+        if (e != cudaSuccess) LLME_REFUSE("attention: cannot reserve %zu bytes of shared memory: %s", DECODE_SMEM, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int G = a.nh / a.nkv;
+    const int chunks = (G + 15) / 16;
+    if ((long long)a.nkv * chunks > 65535) LLME_REFUSE("attention: grid too large");
+    dim3 grid(a.splits, a.nkv * chunks, a.n_rows);
+    attention_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(a);
+    if (a.splits > 1) {
+        const int warps = a.n_rows * a.nh;
+        attention_combine_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(a);
+    }
+    LLME_LAUNCH_STATUS();
+}

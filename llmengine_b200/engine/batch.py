@@ -35,12 +35,14 @@ class StepBatch:
     start_positions: List[int]      # host copy: tokens each request had cached before the step
     token_ids: torch.Tensor         # int32 [T]
     positions: torch.Tensor         # int32 [T] absolute position in the request
-    token_request: torch.Tensor     # int32 [T] row (0..R-1) of the request the token belongs to
+    token_request: torch.Tensor     # int32 [T] block-table row (the state slot) of the token's request
     cu_q_lens: torch.Tensor         # int32 [R+1] prefix sums of q_lens
     ctx_lens: torch.Tensor          # int32 [R] cached length of each request after this step
     state_slots: torch.Tensor       # int32 [R] the request's fixed-size state slot
     first_portion: torch.Tensor     # int32 [R] 1 when the request has nothing cached before this step
     logit_rows: torch.Tensor        # int32 [NL] token rows whose logits are wanted
+    decode_rows: torch.Tensor       # int32 [ND] batch rows of the requests with exactly one token in this step
+    portion_rows: torch.Tensor      # int32 [NP] batch rows of the other requests
     groups: List[GroupView] = field(default_factory=list)
 
     @property
@@ -50,6 +52,14 @@ class StepBatch:
     @property
     def max_ctx_len(self) -> int:
         return max((s + q for s, q in zip(self.start_positions, self.q_lens)), default=0)
+
+    @property
+    def max_portion_len(self) -> int:
+        return max((q for q in self.q_lens if q != 1), default=0)
+
+    @property
+    def max_decode_ctx(self) -> int:
+        return max((s + 1 for s, q in zip(self.start_positions, self.q_lens) if q == 1), default=0)
 
     @property
     def decode_only(self) -> bool:

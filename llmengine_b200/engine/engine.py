@@ -121,7 +121,8 @@ class Engine:
         for n in names:
             self._off[n] = slice(o, o + T)
             o += T
-        for n, ln in (("cu_q_lens", R + 1), ("ctx_lens", R), ("state_slots", R), ("first_portion", R)):
+        for n, ln in (("cu_q_lens", R + 1), ("ctx_lens", R), ("state_slots", R), ("first_portion", R),
+                      ("decode_rows", R), ("portion_rows", R)):
             self._off[n] = slice(o, o + ln)
             o += ln
         self._meta_len = o
@@ -159,6 +160,10 @@ class Engine:
             h[off["state_slots"]][r] = st.slot
             h[off["first_portion"]][r] = 1 if s == 0 else 0
         h[off["cu_q_lens"]][: R + 1] = cu
+        dec = [r for r, q in enumerate(q_lens) if q == 1]
+        por = [r for r, q in enumerate(q_lens) if q != 1]
+        h[off["decode_rows"]][:len(dec)] = dec
+        h[off["portion_rows"]][:len(por)] = por
         NL = len(rows)
         h[off["logit_rows"]][:NL] = np.asarray(rows, dtype=np.int32) if NL else 0
         self._meta_dev.copy_(self._staging[i], non_blocking=True)
@@ -177,7 +182,8 @@ class Engine:
             num_tokens=T, num_requests=R, q_lens=q_lens, start_positions=list(starts),
             token_ids=view("token_ids", T), positions=view("positions", T), token_request=view("token_request", T),
             cu_q_lens=view("cu_q_lens", R + 1), ctx_lens=view("ctx_lens", R), state_slots=view("state_slots", R),
-            first_portion=view("first_portion", R), logit_rows=view("logit_rows", NL), groups=groups)
+            first_portion=view("first_portion", R), logit_rows=view("logit_rows", NL),
+            decode_rows=view("decode_rows", len(dec)), portion_rows=view("portion_rows", len(por)), groups=groups)
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], end: Sequence[Hashable] = ()) -> Optional[torch.Tensor]:

@@ -1,0 +1,82 @@
+"""Command line in the manner of the reference's `generate`
+(examples/generate.cpp:57-65: `generate <model.gguf> [prompt] [max_tokens]`, prompt "Hello",
+max_tokens 64, greedy, progress on stderr, result on stdout, `[Generated N tokens total]`).
+
+    python -m llmengine_b200.generate <model_dir> [prompt] [max_tokens] [options]
+
+This engine works on token ids (it has no tokenizer), so `prompt` is a list of ids separated by
+commas or spaces, default "1".  Several prompts may be given separated by ';'.  The sampling
+options carry the names of the reference's SamplingConfig fields.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+from typing import List, Optional
+
+
+def parse_prompts(text: str) -> List[List[int]]:
+    out = []
+    for part in text.split(";"):
+        ids = [int(x) for x in part.replace(",", " ").split()]
+        if ids:
+            out.append(ids)
+    if not out:
+        raise ValueError("the prompt holds no token ids")
+    return out
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="generate", description=__doc__.split("\n\n")[0])
+    ap.add_argument("model", help="folder with config.json and model.safetensors")
+    ap.add_argument("prompt", nargs="?", default="1", help="token ids, e.g. \"5,17,3\"; ';' separates prompts")
+    ap.add_argument("max_tokens", nargs="?", type=int, default=64)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--greedy", dest="greedy", action="store_true", default=True)
+    ap.add_argument("--no-greedy", dest="greedy", action="store_false", help="draw from the distribution")
+    ap.add_argument("--temperature", type=float, default=1.0)
+    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--top-p", type=float, default=0.0)
+    ap.add_argument("--repetition-penalty", type=float, default=1.0)
+    ap.add_argument("--seed", type=int, default=42)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-cached-tokens", type=int, default=0, help="cache pool in tokens (0 = from free memory)")
+    ap.add_argument("--max-num-seqs", type=int, default=64)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=2048)
+    ap.add_argument("--prefill-chunk", type=int, default=2048)
+    ap.add_argument("--kernels", choices=["fast", "plain"], default="fast")
+    ap.add_argument("--ignore-eos", action="store_true")
+    args = ap.parse_args(argv)
+
+    from .engine.llm import LLM
+    from .sampling import SamplingParams
+
+    def log(msg: str) -> None:
+        print(msg, file=sys.stderr, flush=True)
+
+    prompts = parse_prompts(args.prompt)
+    log("[1/3] Loading model...")
+    t0 = time.time()
+    llm = LLM(args.model, dtype=args.dtype, page_size=args.page_size, max_cached_tokens=args.max_cached_tokens,
+              max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
+              prefill_chunk=args.prefill_chunk, kernels=args.kernels, seed=args.seed)
+    log(f"      {time.time() - t0:.1f} s")
+    sp = SamplingParams(greedy=args.greedy, top_k=args.top_k, top_p=args.top_p, temperature=args.temperature,
+                        repetition_penalty=args.repetition_penalty, seed=args.seed)
+    log(f"[2/3] Generating ({len(prompts)} prompt(s), up to {args.max_tokens} tokens each)...")
+    t0 = time.time()
+    outs = llm.generate(prompts, sp, args.max_tokens, eos_token_id=None if args.ignore_eos else "model")
+    dt = time.time() - t0
+    log("[3/3] Done")
+    total = 0
+    for o in outs:
+        print(" ".join(str(t) for t in o.token_ids))
+        total += len(o.token_ids)
+    print(f"\n[Generated {total} tokens total]")
+    log(f"      {total / max(dt, 1e-9):.1f} tokens/s")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

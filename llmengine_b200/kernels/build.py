@@ -28,6 +28,13 @@ SOURCES: Dict[str, str] = {
     "attention_plain": "attention_plain.cu",
     "gemm_f32": "gemm_f32.cu",
     "sampling": "sampling.cu",
+    # compiled per head size: ask for "attention_fast@HEAD_DIM=128"
+    "attention_fast": "attention_fast.cu",
+}
+
+# libraries that need compile-time values, and the values `build_all` compiles them for
+VARIANTS: Dict[str, List[str]] = {
+    "attention_fast": ["attention_fast@HEAD_DIM=64", "attention_fast@HEAD_DIM=128"],
 }
 
 NVCC_FLAGS = [
@@ -68,9 +75,21 @@ def build_dir() -> str:
         return d
 
 
-def _digest(name: str) -> str:
+def split_key(key: str):
+    """"name@A=1,B=2" -> ("name", ["-DA=1", "-DB=2"])."""
+    name, _, rest = key.partition("@")
+    if name not in SOURCES:
+        raise BuildError(f"no kernel library named {name!r}; known: {', '.join(sorted(SOURCES))}")
+    defines = [f"-D{d}" for d in rest.split(",") if d]
+    if name in VARIANTS and not defines:
+        raise BuildError(f"library {name!r} needs compile-time values, e.g. {VARIANTS[name][0]!r}")
+    return name, defines
+
+
+def _digest(key: str) -> str:
+    name, defines = split_key(key)
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + defines).encode())
     for fn in sorted(os.listdir(CSRC)):
         if fn.endswith((".cuh", ".h")) or fn == SOURCES[name]:
             with open(os.path.join(CSRC, fn), "rb") as f:
@@ -79,10 +98,10 @@ def _digest(name: str) -> str:
     return h.hexdigest()[:12]
 
 
-def library_path(name: str) -> str:
-    if name not in SOURCES:
-        raise BuildError(f"no kernel library named {name!r}; known: {', '.join(sorted(SOURCES))}")
-    return os.path.join(build_dir(), f"llme_{name}_{_digest(name)}.so")
+def library_path(key: str) -> str:
+    name, defines = split_key(key)
+    tag = "".join("_" + d[2:].replace("=", "") for d in defines)
+    return os.path.join(build_dir(), f"llme_{name}{tag}_{_digest(key)}.so")
 
 
 def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) -> Dict[str, str]:
@@ -97,8 +116,9 @@ def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) 
     t0 = time.time()
     for n in todo:
         tmp = f"{paths[n]}.{os.getpid()}.tmp"
-        cmd = [nvcc, *NVCC_FLAGS, *(extra_flags or []), "-I", CSRC, "-o", tmp, os.path.join(CSRC, SOURCES[n])]
-        _log(f"compiling {SOURCES[n]} for sm_100a ...")
+        name, defines = split_key(n)
+        cmd = [nvcc, *NVCC_FLAGS, *defines, *(extra_flags or []), "-I", CSRC, "-o", tmp, os.path.join(CSRC, SOURCES[name])]
+        _log(f"compiling {SOURCES[name]} {' '.join(defines)} for sm_100a ...".replace("  ", " "))
         procs[n] = (subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True), tmp)
     last = time.time()
     pending = dict(procs)
@@ -111,7 +131,7 @@ def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) 
             if p.returncode != 0:
                 for _, (q, qtmp) in pending.items():
                     q.kill()
-                raise BuildError(f"nvcc failed on {SOURCES[n]} (exit {p.returncode}):\n{out}")
+                raise BuildError(f"nvcc failed on {n} (exit {p.returncode}):\n{out}")
             os.replace(tmp, paths[n])
             _log(f"built {os.path.basename(paths[n])} in {time.time() - t0:.0f} s")
         if pending:
@@ -123,4 +143,7 @@ def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) 
 
 
 def build_all() -> Dict[str, str]:
-    return ensure_built(list(SOURCES))
+    keys = [n for n in SOURCES if n not in VARIANTS]
+    for v in VARIANTS.values():
+        keys.extend(v)
+    return ensure_built(keys)

@@ -62,6 +62,15 @@ class _AttnArgs(Structure):
     ]
 
 
+class _FastAttnArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("cache", c_void_p), ("out", c_void_p), ("rows", c_void_p), ("cu_q_lens", c_void_p),
+        ("ctx_lens", c_void_p), ("table_rows", c_void_p), ("block_tables", c_void_p), ("scratch", c_void_p),
+        ("max_blocks", c_int), ("n_rows", c_int), ("nh", c_int), ("nkv", c_int), ("page_size", c_int),
+        ("window", c_int), ("splits", c_int), ("scale", c_float),
+    ]
+
+
 class _SampleArgs(Structure):
     _fields_ = [
         ("logits", c_void_p), ("ld", c_longlong), ("rows", c_int), ("vocab", c_int),
@@ -181,6 +190,57 @@ class CudaOps:
         rc = lib.llme_attention_plain(byref(a), c_int(_code(q.dtype)), self._stream())
         self._check(lib, rc, "attention_plain")
         return out
+
+    @staticmethod
+    def fast_attention_supports(head_dim: int, dtype: torch.dtype) -> bool:
+        return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+    def _fast_lib(self, head_dim: int) -> ctypes.CDLL:
+        key = f"attention_fast@HEAD_DIM={head_dim}"
+        lib = self._lib(key)
+        if not getattr(lib, "_llme_ready", False):
+            lib.llme_attention_decode_scratch_floats.restype = c_longlong
+            assert lib.llme_attention_head_dim() == head_dim
+            lib._llme_ready = True
+        return lib
+
+    def _fast_args(self, q, cache, out, rows, cu_q_lens, ctx_lens, table_rows, block_tables, num_heads, num_kv_heads,
+                   page_size, window, scale, splits=1, scratch=None) -> "_FastAttnArgs":
+        assert q.dtype == cache.dtype == out.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous()
+        assert block_tables.is_contiguous() and cache.is_contiguous()
+        return _FastAttnArgs(q.data_ptr(), cache.data_ptr(), out.data_ptr(), rows.data_ptr(), cu_q_lens.data_ptr(),
+                             ctx_lens.data_ptr(), table_rows.data_ptr(), block_tables.data_ptr(), _ptr(scratch),
+                             block_tables.shape[1], rows.numel(), num_heads, num_kv_heads, page_size, window, splits,
+                             scale)
+
+    def attention_portions(self, *, q, cache, out, rows, cu_q_lens, ctx_lens, table_rows, block_tables, num_heads: int,
+                           num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                           max_q_len: int) -> None:
+        """Tensor-core attention for the requests `rows` of the batch, each with a portion of any length."""
+        lib = self._fast_lib(head_dim)
+        a = self._fast_args(q, cache, out, rows, cu_q_lens, ctx_lens, table_rows, block_tables, num_heads,
+                            num_kv_heads, page_size, window, scale)
+        rc = lib.llme_attention_portion(byref(a), c_int(max_q_len), self._stream())
+        self._check(lib, rc, "attention_portions")
+
+    def attention_decode_scratch_floats(self, head_dim: int, n_rows: int, num_heads: int, splits: int) -> int:
+        return int(self._fast_lib(head_dim).llme_attention_decode_scratch_floats(c_int(n_rows), c_int(num_heads), c_int(splits)))
+
+    def attention_decode(self, *, q, cache, out, rows, cu_q_lens, ctx_lens, table_rows, block_tables, num_heads: int,
+                         num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, splits: int,
+                         scratch: Optional[torch.Tensor]) -> None:
+        """Tensor-core attention for the requests `rows`, each with exactly one new token; the context
+        of each is split over `splits` blocks whose partial results meet in `scratch`."""
+        lib = self._fast_lib(head_dim)
+        if splits > 1:
+            need = self.attention_decode_scratch_floats(head_dim, rows.numel(), num_heads, splits)
+            assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need
+        a = self._fast_args(q, cache, out, rows, cu_q_lens, ctx_lens, table_rows, block_tables, num_heads,
+                            num_kv_heads, page_size, window, scale, splits, scratch)
+        rc = lib.llme_attention_decode(byref(a), self._stream())
+        self._check(lib, rc, "attention_decode")
+        if splits > 1:
+            self.launches += 1
 
     def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         lib = self._lib("elementwise")

@@ -100,7 +100,35 @@ class GQAttention(Part):
         return ops.linear(out, self.w_o, delta)
 
     def attend(self, q, kv, out, batch, group) -> None:
-        ops = self.rt.ops
-        ops.attention_plain(q=q, cache=kv, out=out, positions=batch.positions, token_request=batch.token_request,
-                            block_tables=group.block_tables, num_heads=self.nh, num_kv_heads=self.nkv,
-                            head_dim=self.hd, page_size=group.page_size, window=self.window, scale=self.scale)
+        """Attention of every token of the batch over its request's cache.  bfloat16 with head sizes
+        the tensor-core kernels are built for: requests with one new token go to the split-context
+        decode kernel, the others to the portion kernel.  Everything else (32-bit, other head sizes,
+        `kernels="plain"`) goes to the plain kernel, which serves every case."""
+        rt, ops = self.rt, self.rt.ops
+        common = dict(q=q, cache=kv, out=out, block_tables=group.block_tables, num_heads=self.nh,
+                      num_kv_heads=self.nkv, head_dim=self.hd, page_size=group.page_size, window=self.window,
+                      scale=self.scale)
+        fast = (rt.kernels == "fast" and hasattr(ops, "fast_attention_supports")
+                and ops.fast_attention_supports(self.hd, q.dtype))
+        if not fast:
+            ops.attention_plain(positions=batch.positions, token_request=batch.token_request, **common)
+            return
+        meta = dict(cu_q_lens=batch.cu_q_lens, ctx_lens=batch.ctx_lens, table_rows=batch.state_slots)
+        n_dec = batch.decode_rows.numel()
+        if batch.portion_rows.numel():
+            ops.attention_portions(rows=batch.portion_rows, max_q_len=batch.max_portion_len, **meta, **common)
+        if n_dec:
+            splits = self.decode_splits(n_dec, batch.max_decode_ctx)
+            scratch = None
+            if splits > 1:
+                need = ops.attention_decode_scratch_floats(self.hd, n_dec, self.nh, splits)
+                scratch = rt.buffer("attention_scratch", 1, need, torch.float32, exact=True)
+            ops.attention_decode(rows=batch.decode_rows, splits=splits, scratch=scratch, **meta, **common)
+
+    def decode_splits(self, n_requests: int, max_ctx: int) -> int:
+        """Blocks per (request, key/value head): enough to give every SM about two blocks, never more
+        than there are 64-key tiles in the longest (windowed) context."""
+        span = min(max_ctx, self.window) if self.window > 0 else max_ctx
+        tiles = max(1, -(-span // 64) + (1 if self.window > 0 else 0))
+        blocks = n_requests * self.nkv * (-(-(self.nh // self.nkv) // 16))
+        return max(1, min(tiles, -(-2 * 148 // blocks), 64))

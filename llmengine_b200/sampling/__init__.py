@@ -1,0 +1,4 @@
+"""Sampling options and the device sampler."""
+from .sampler import Sampler, SamplingParams, uniform
+
+__all__ = ["Sampler", "SamplingParams", "uniform"]

@@ -217,7 +217,13 @@ def _attention_case(nh, nkv, hd, page, ctx_lens, q_lens, window, dtype, seed, sp
             positions.append(p)
             token_req.append(r + 1)
             want.append(full[p].reshape(-1))
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
     return dict(
+        cu_q_lens=torch.tensor(cu, dtype=torch.int32, device=DEV),
+        ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+        table_rows=torch.arange(1, R + 1, dtype=torch.int32, device=DEV),
         q=torch.stack(q_rows).to(dtype).to(DEV), cache=cache.to(DEV),
         positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
         token_request=torch.tensor(token_req, dtype=torch.int32, device=DEV),
@@ -259,6 +265,65 @@ def test_attention_plain_finds_the_one_key_that_matters(ops, where):
                         token_request=case["token_request"], block_tables=case["block_tables"], num_heads=nh,
                         num_kv_heads=nkv, head_dim=hd, page_size=page, window=window, scale=1 / math.sqrt(hd))
     assert (out.cpu() - case["want"]).abs().max() < 2e-5
+
+
+def _run_fast(ops, case, nh, nkv, hd, page, window, q_lens, splits=None):
+    out = torch.full_like(case["q"], float("nan"))
+    common = dict(q=case["q"], cache=case["cache"], out=out, cu_q_lens=case["cu_q_lens"], ctx_lens=case["ctx_lens"],
+                  table_rows=case["table_rows"], block_tables=case["block_tables"], num_heads=nh, num_kv_heads=nkv,
+                  head_dim=hd, page_size=page, window=window, scale=1 / math.sqrt(hd))
+    dec = [r for r, n in enumerate(q_lens) if n == 1]
+    por = [r for r, n in enumerate(q_lens) if n != 1]
+    if por:
+        ops.attention_portions(rows=torch.tensor(por, dtype=torch.int32, device=DEV), max_q_len=max(q_lens), **common)
+    if dec:
+        sp = splits or 3
+        need = ops.attention_decode_scratch_floats(hd, len(dec), nh, sp)
+        scratch = torch.full((max(need, 1),), float("nan"), device=DEV)
+        ops.attention_decode(rows=torch.tensor(dec, dtype=torch.int32, device=DEV), splits=sp, scratch=scratch, **common)
+    return out
+
+
+FAST_SHAPES = [(4, 2, 16, 8), (6, 3, 48, 16), (8, 1, 80, 4), (8, 2, 128, 16), (3, 3, 32, 16), (16, 4, 64, 32),
+               (40, 2, 64, 16), (32, 8, 128, 16)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", FAST_SHAPES)
+@pytest.mark.parametrize("window", [0, 13, 100])
+def test_attention_fast_mixed_batch(ops, nh, nkv, hd, page, window):
+    """Portions of several lengths (one request whole, one deep into its context, one of two tokens)
+    beside single decoded tokens, in one batch; unwritten cache rows hold NaN."""
+    ctx_lens = [1, 37, 64, 150, 333, 65, 700]
+    q_lens = [1, 37, 1, 9, 200, 2, 1]
+    case = _attention_case(nh, nkv, hd, page, ctx_lens, q_lens, window, torch.bfloat16, 30)
+    out = _run_fast(ops, case, nh, nkv, hd, page, window, q_lens)
+    assert torch.isfinite(out).all()
+    assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("splits", [1, 2, 7, 64])
+def test_attention_decode_any_number_of_splits(ops, splits):
+    nh, nkv, hd, page = 8, 2, 128, 16
+    ctx_lens, q_lens = [5, 64, 65, 1000], [1, 1, 1, 1]
+    case = _attention_case(nh, nkv, hd, page, ctx_lens, q_lens, 0, torch.bfloat16, 31)
+    out = _run_fast(ops, case, nh, nkv, hd, page, 0, q_lens, splits=splits)
+    assert torch.isfinite(out).all()
+    assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("q_len", [1, 40])
+@pytest.mark.parametrize("where", ["far_back", "page_last", "page_first", "tile_last", "tile_first", "window_inside",
+                                   "window_outside"])
+def test_attention_fast_finds_the_one_key_that_matters(ops, where, q_len):
+    nh, nkv, hd, page, ctx, window = 8, 2, 64, 16, 700, 0
+    key = {"far_back": 3, "page_last": 16 * 20 - 1, "page_first": 16 * 20, "tile_last": 64 * 5 - 1,
+           "tile_first": 64 * 5}.get(where)
+    if where.startswith("window"):
+        window = 100
+        key = ctx - 100 if where == "window_inside" else ctx - 101
+    case = _attention_case(nh, nkv, hd, page, [ctx], [q_len], window, torch.bfloat16, 32, spike=(0, key))
+    out = _run_fast(ops, case, nh, nkv, hd, page, window, [q_len], splits=4)
+    assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -21,10 +21,19 @@ from tiny_configs import TINY_A, TINY_B, TINY_C
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 # Largest |logit difference| allowed against the plain implementation.  Logits of these models
-# are of order 1.  32-bit: sums in another order.  bfloat16: the plain implementation rounds
-# at the same places, what remains is the order of sums and values that fall on the other side
-# of a rounding step.
-TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+# are of order 1.  32-bit: only the order of sums differs, 1e-4 at most.  bfloat16: the plain
+# implementation rounds at the same places as the engine, but a value that falls on the other side
+# of a rounding step is then carried on, and a model with sharp attention amplifies it.  How much a
+# given model amplifies rounding is measured on the plain implementation itself (its bfloat16-rounded
+# run against its 32-bit run); the engine may differ from the rounded plain run by 0.6 of that, and
+# by 1e-2 at least.  (Measured: the engine stays within 0.3 to 0.4 of it where that exceeds 1e-2.)
+TOL_F32 = 1e-4
+
+
+def bf16_tolerance(ref16, ref32):
+    inherent = max(float((ref16[r] - ref32[r]).abs().max()) for r in ref16)
+    return max(1e-2, 0.6 * inherent)
+
 
 CONFIGS = {
     "A": (TINY_A, 16, [70, 33, 100, 19, 45, 64, 7]),
@@ -37,9 +46,14 @@ def _setup(tmp_path, name, dtype, sharpen):
     cfg, page, lens = CONFIGS[name]
     d = make_model_dir(str(tmp_path / f"{name}_{dtype}"), cfg, seed=11, dtype="bfloat16", sharpen=sharpen)
     reqs = {f"r{i}": random_ids(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(lens)}
-    plain = PlainQwen3(d, round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    plain = PlainQwen3(d)
     ref = {r: plain.logits(ids) for r, ids in reqs.items()}
-    return d, page, reqs, ref
+    tol = TOL_F32
+    if dtype == "bfloat16":
+        rounded = PlainQwen3(d, round_to=torch.bfloat16)
+        ref16 = {r: rounded.logits(ids) for r, ids in reqs.items()}
+        tol, ref = bf16_tolerance(ref16, ref), ref16
+    return d, page, reqs, ref, tol
 
 
 def _traces(reqs):
@@ -53,13 +67,13 @@ def _traces(reqs):
 
 
 def _run_all(tmp_path, name, dtype, sharpen, ops, device):
-    d, page, reqs, ref = _setup(tmp_path, name, dtype, sharpen)
+    d, page, reqs, ref, tol = _setup(tmp_path, name, dtype, sharpen)
     worst = {}
     for what, steps in _traces(reqs).items():
         pool = max_live_tokens(steps, 64)
         eng = engine_for(d, dtype, pool, page_size=page, ops=ops, device=device)
         got = replay(eng, steps, poison=True)
-        worst[what] = compare(got, ref, TOL[dtype], f"{name}/{dtype}/{what}")
+        worst[what] = compare(got, ref, tol, f"{name}/{dtype}/{what}")
         eng.cache.check_invariants()
         assert not eng.cache.requests, "every request was ended, nothing may be held"
         assert all(g.pool.free_count == g.pool.num_pages for g in eng.cache.groups)
@@ -73,10 +87,11 @@ def test_host_logic_replay_cpu(tmp_path, name):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("sharpen", [1.0, 3.0])
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype,sharpen", [("float32", 1.0), ("float32", 3.0), ("bfloat16", 1.0), ("bfloat16", 2.0)])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_replay_gpu(tmp_path, name, dtype, sharpen):
+    """`sharpen` scales the QK-norm gains: attention becomes peaked, so that a key that is skipped,
+    read from a wrong page or seen through a wrong mask moves the logits by far more than the tolerance."""
     worst = _run_all(tmp_path, name, dtype, sharpen, None, "cuda:0")
     print(f"replay {name} {dtype} sharpen={sharpen}: " + ", ".join(f"{k} {v:.2e}" for k, v in worst.items()))
 
@@ -85,7 +100,7 @@ def test_replay_gpu(tmp_path, name, dtype, sharpen):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(tmp_path, dtype):
     """The program itself, as a user calls it: JSON lines in, <step>.f32 files and `done` lines out."""
-    d, page, reqs, ref = _setup(tmp_path, "B", dtype, 2.0)
+    d, page, reqs, ref, tol = _setup(tmp_path, "B", dtype, 2.0)
     steps = _traces(reqs)["mixed"]
     out = tmp_path / "out"
     lines = [json.dumps({"step": i, "entries": [{"id": r, "tokens": t, "want": w} for r, t, w in e], "end": end})
@@ -104,4 +119,4 @@ def test_trace_run_program(tmp_path, dtype):
             rows.setdefault(r, []).append(arr[k:k + len(w)])
             k += len(w)
         assert k == arr.shape[0]
-    compare({r: torch.cat(v) for r, v in rows.items()}, ref, TOL[dtype], f"trace_run/{dtype}")
+    compare({r: torch.cat(v) for r, v in rows.items()}, ref, tol, f"trace_run/{dtype}")
