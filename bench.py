@@ -1,0 +1,275 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one GPU, as one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the third configuration of BASELINE.json): Qwen3-8B layer sizes, random weights,
+bfloat16; a decode step for a batch of 8 requests that each hold 2,048 cached tokens (context
+length 4,096: they could go on to 4,096), plus decode at batch 1 and 64 and one prefill of a
+2,048-token prompt.  Token ids are synthetic, uniform over the vocabulary.
+
+`value` is decoded tokens per second timed on the device with CUDA events around exactly K
+steps (after W warm-up steps).  `e2e` is the same through the Python entry point (`LLM.step`),
+host token ids in and host token ids out every step, timed on the host clock around
+synchronised steps.  Every decode step reads all weights (15 GB) and the live cache, far more
+than the L2 holds, so no explicit L2 flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 36, "hidden_size": 4096,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+    "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 40960, "hidden_act": "silu",
+}
+CONTEXT = 4096          # benchmark context length
+CACHED = 2048           # tokens each request holds when decoding is timed
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    """Measured peaks of this pool if the driver wrote them, else the fallback figures."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        if "hbm_gbs" in d:
+            out["hbm_gbs"] = float(d["hbm_gbs"])
+        if "bf16_tflops" in d:
+            out["bf16_tflops"] = float(d["bf16_tflops"])
+        out["source"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", "0", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def mark(self):
+        return time.time()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, t0, t1):
+        sm, mx, reasons = [], [], set()
+        for t, line in self.samples:
+            if not (t0 - 0.05 <= t <= t1 + 0.15):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args) -> int:
+    # The reference is a CMake/C++ project without any Python packaging (no setup.py, no pyproject.toml),
+    # so the offline `pip install --target baseline/_ref /root/reference` has nothing to build; its
+    # generate_cuda example also needs a GGUF file with tokenizer metadata and runs one sequence at a
+    # time, so the batch-8 metric on random Qwen3-8B weights cannot be produced through its stock path.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "the reference is a CMake C++ project with no Python package to pip-install offline, and its "
+                      "stock generate path needs a GGUF model file with tokenizer and decodes one sequence at a time"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=MODEL_8B["num_hidden_layers"],
+                    help="fewer layers than the model has (the record then names both numbers)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-graphs", action="store_true", help="do not capture decode steps in CUDA graphs")
+    ap.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the end-to-end run")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from llmengine_b200 import LLM, SamplingParams
+    from llmengine_b200.config import EngineConfig
+    from llmengine_b200.engine.engine import StepEntry
+
+    cfg = dict(MODEL_8B)
+    cfg["num_hidden_layers"] = args.layers
+    max_batch = 64 if not args.skip_points else args.batch
+    ec = EngineConfig(dtype="bfloat16", page_size=16, max_cached_tokens=max_batch * CONTEXT, max_num_seqs=max_batch,
+                      max_num_batched_tokens=max(PREFILL_TOKENS, max_batch), prefill_chunk=PREFILL_TOKENS,
+                      max_model_len=CONTEXT, use_cuda_graphs=not args.no_graphs)
+    llm = LLM(config=cfg, random_seed=0, engine_config=ec)
+    eng = llm.engine
+    ops = eng.ops
+    V = cfg["vocab_size"]
+    gen = torch.Generator().manual_seed(0)
+
+    def tokens(n):
+        return torch.randint(0, V, (n,), generator=gen).tolist()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = ops.launches
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps, ops.launches - l0
+
+    clocks = ClockSampler()
+    clocks.start()
+
+    # ---- prefill: one 2,048-token prompt per step (each leaves a request with 2,048 cached tokens)
+    prompt = tokens(PREFILL_TOKENS)
+    counter = [0]
+
+    def prefill_once():
+        name = f"p{counter[0]}"
+        counter[0] += 1
+        eng.step([StepEntry(name, prompt, [PREFILL_TOKENS - 1])], end=[name])
+
+    prefill_ms, _ = timed(prefill_once, 5, 3)
+
+    # ---- decode at a given batch: requests that hold CACHED tokens, one new token each per step
+    sp = SamplingParams(greedy=True)
+
+    def decode_bench(batch, steps, warmup):
+        names = [f"d{batch}_{i}" for i in range(batch)]
+        for n in names:
+            eng.step([StepEntry(n, tokens(CACHED), [])])
+        feed = [tokens(1) for _ in range(batch)]
+
+        def one():
+            logits = eng.step([StepEntry(n, t, [0]) for n, t in zip(names, feed)])
+            llm.sampler.sample(logits, [sp] * batch, [0] * batch)
+
+        t0 = clocks.mark()
+        ms, launches = timed(one, steps, warmup)
+        t1 = clocks.mark()
+        ctx = CACHED + warmup + steps // 2          # mean cached length over the timed steps
+        for n in names:
+            eng.free(n)
+        return ms, launches, ctx, (t0, t1)
+
+    ms, launches, ctx, window = decode_bench(args.batch, args.steps, args.warmup)
+    points = {}
+    e2e = None
+    if not args.skip_points:
+        for b in (1, 64):
+            m, _, _, _ = decode_bench(b, max(16, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
+
+        # ---- end to end through the Python entry point: host tokens in, host tokens out, every step
+        ids = [llm.add_request(tokens(CACHED), sp, max_tokens=args.warmup + args.steps + 2, eos_token_id=None)
+               for _ in range(args.batch)]
+        while any(llm.scheduler.state(i).phase.value != "decoding" for i in ids):
+            llm.step()
+        for _ in range(args.warmup):
+            llm.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            llm.step()                               # ends with the device-to-host read of the sampled tokens
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        e2e = {"value": round(args.batch * args.steps / dt, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(eng._meta_len * 4 + llm.sampler._host.numel() * 4),
+               "d2h_bytes_per_step": int(args.batch * 4)}
+    clocks.stop()
+
+    # ---- roofline of the decode step: every weight it uses once + the cache of the live requests
+    L, H, I = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nh + 2 * nkv) * hd * H + H * nh * hd + 3 * H * I + 2 * H + 2 * hd
+    weight_bytes = 2 * (L * per_layer + V * H + H) + 2 * args.batch * H       # + the embedding rows that are read
+    kv_bytes = args.batch * ctx * L * 2 * nkv * hd * 2
+    pk = peaks()
+    achieved = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+    T = PREFILL_TOKENS
+    prefill_flops = 2 * T * L * per_layer + 2 * V * H + L * 4 * nh * hd * T * (T + 1) / 2
+    prefill = {"value": round(T * 1000.0 / prefill_ms, 1), "tokens": T, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    value = args.batch * 1000.0 / ms
+    rec = {
+        "metric": "decode tokens/s, Qwen3-8B shape bf16, batch 8, 2048 cached tokens per request",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids, random weights",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": args.layers, "layers_of_model": MODEL_8B["num_hidden_layers"],
+            "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": I, "vocab": V,
+            "global_batch": args.batch, "seq_len": CONTEXT, "cached_tokens": CACHED, "page_size": 16,
+            "parallelism": "single GPU", "cuda_graphs": bool(getattr(eng, "graphs_enabled", False)),
+            "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": pk["source"],
+        },
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "e2e": e2e,
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(*window),
+    }
+    print(json.dumps(rec))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
