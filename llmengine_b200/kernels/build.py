@@ -30,11 +30,17 @@ SOURCES: Dict[str, str] = {
     "sampling": "sampling.cu",
     # compiled per head size: ask for "attention_fast@HEAD_DIM=128"
     "attention_fast": "attention_fast.cu",
+    # the same kernels with built-in scratch memory: "attention_decode_static@HEAD_DIM=128"
+    "attention_decode_static": "attention_decode_static.cu",
 }
+
+# sources that a library's source file includes (they count for its hash)
+INCLUDES: Dict[str, List[str]] = {"attention_decode_static": ["attention_fast.cu"]}
 
 # libraries that need compile-time values, and the values `build_all` compiles them for
 VARIANTS: Dict[str, List[str]] = {
     "attention_fast": ["attention_fast@HEAD_DIM=64", "attention_fast@HEAD_DIM=128"],
+    "attention_decode_static": ["attention_decode_static@HEAD_DIM=128"],
 }
 
 NVCC_FLAGS = [
@@ -91,7 +97,7 @@ def _digest(key: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS + defines).encode())
     for fn in sorted(os.listdir(CSRC)):
-        if fn.endswith((".cuh", ".h")) or fn == SOURCES[name]:
+        if fn.endswith((".cuh", ".h")) or fn == SOURCES[name] or fn in INCLUDES.get(name, ()):
             with open(os.path.join(CSRC, fn), "rb") as f:
                 h.update(fn.encode())
                 h.update(f.read())
