@@ -1,0 +1,136 @@
+"""On the GPU: generation through the Python entry point and the command line, long decoding
+one token at a time from the very first token, and drawn tokens from a fixed seed."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import compare, engine_for, make_model_dir, random_ids, replay
+from llmengine_b200 import LLM, SamplingParams
+from llmengine_b200.sampling import uniform
+from plain_model import PlainQwen3, plain_sample
+from tiny_configs import TINY_A, TINY_B, TINY_C
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _check_greedy(plain, prompt, tokens, margin):
+    """Every generated token is the plain implementation's argmax given the tokens before it, or (for
+    bfloat16) a token whose plain logit is within `margin` of that maximum."""
+    ids = list(prompt)
+    for t in tokens:
+        row = plain.logits(ids)[-1]
+        best = int(row.argmax())
+        assert t == best or float(row[best] - row[t]) <= margin, (len(ids), t, best, float(row[best] - row[t]))
+        ids.append(t)
+
+
+@pytest.mark.parametrize("dtype,margin", [("float32", 1e-4), ("bfloat16", 3e-2)])
+@pytest.mark.parametrize("cfg,page,chunk", [(TINY_A, 16, 64), (TINY_B, 8, 48), (TINY_C, 16, 40)])
+def test_greedy_generation_through_the_entry_point(tmp_path, cfg, page, chunk, dtype, margin):
+    d = make_model_dir(str(tmp_path / "m"), cfg, 5, dtype="bfloat16", sharpen=1.5)
+    llm = LLM(d, dtype=dtype, page_size=page, max_cached_tokens=1024, max_num_seqs=4, max_num_batched_tokens=64,
+              prefill_chunk=chunk)
+    prompts = [random_ids(n, cfg["vocab_size"], i) for i, n in enumerate([1, 5, 64, 130, 33, 7])]
+    outs = llm.generate(prompts, SamplingParams(greedy=True), max_tokens=16, eos_token_id=None)
+    plain = PlainQwen3(d)
+    for p, o in zip(prompts, outs):
+        assert len(o.token_ids) == 16 and o.finish_reason == "length"
+        _check_greedy(plain, p, o.token_ids, margin)
+    llm.engine.cache.check_invariants()
+    assert not llm.engine.cache.requests
+    assert llm.engine.ops.launches > 0
+
+
+def test_cuda_graph_decoding_gives_the_same_tokens(tmp_path):
+    d = make_model_dir(str(tmp_path / "m"), TINY_B, 8, dtype="bfloat16", sharpen=1.5)
+    prompts = [random_ids(n, 1000, i) for i, n in enumerate([9, 40, 3])]
+    runs = []
+    for graphs in (False, True):
+        llm = LLM(d, dtype="bfloat16", page_size=8, max_cached_tokens=1024, max_num_seqs=4, max_num_batched_tokens=64,
+                  use_cuda_graphs=graphs)
+        runs.append([o.token_ids for o in llm.generate(prompts, max_tokens=40, eos_token_id=None)])
+    assert runs[0] == runs[1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_from_the_first_token(tmp_path, dtype):
+    """One token a step from position 0 on, for 230 steps, two requests side by side: the first tokens
+    of a sequence, every page edge and a long run of single-token steps."""
+    d = make_model_dir(str(tmp_path / "m"), TINY_A, 6, dtype="bfloat16", sharpen=2.0)
+    reqs = {"a": random_ids(230, 512, 1), "b": random_ids(190, 512, 2)}
+    steps = []
+    for i in range(230):
+        entries = [(r, ids[i:i + 1], [0]) for r, ids in reqs.items() if i < len(ids)]
+        steps.append((entries, [r for r, ids in reqs.items() if i == len(ids) - 1]))
+    eng = engine_for(d, dtype, 512, page_size=16)
+    got = replay(eng, steps, poison=True)
+    if dtype == "float32":
+        plain = PlainQwen3(d)
+        compare(got, {r: plain.logits(ids) for r, ids in reqs.items()}, 1e-4, "long decode")
+    else:
+        from test_replay import bf16_tolerance
+        p32, p16 = PlainQwen3(d), PlainQwen3(d, round_to=torch.bfloat16)
+        ref16 = {r: p16.logits(ids) for r, ids in reqs.items()}
+        compare(got, ref16, bf16_tolerance(ref16, {r: p32.logits(ids) for r, ids in reqs.items()}), "long decode bf16")
+
+
+def test_drawn_tokens_from_a_fixed_seed(tmp_path):
+    """Temperature 0.7 from a fixed seed (32-bit): the tokens are those of the plain sampler fed the
+    plain logits and the same uniform numbers, whatever else is in the batch."""
+    d = make_model_dir(str(tmp_path / "m"), TINY_B, 7, dtype="bfloat16")
+    llm = LLM(d, dtype="float32", page_size=8, max_cached_tokens=1024, max_num_seqs=4, max_num_batched_tokens=64,
+              prefill_chunk=48)
+    prompts = [random_ids(n, 1000, 10 + i) for i, n in enumerate([1, 5, 64, 130, 200])]
+    sps = [SamplingParams(greedy=False, temperature=0.7, seed=1000 + i) for i in range(5)]
+    outs = llm.generate(prompts, sps, max_tokens=24, eos_token_id=None)
+    plain = PlainQwen3(d)
+    for p, sp, o in zip(prompts, sps, outs):
+        ids = list(p)
+        for i, t in enumerate(o.token_ids):
+            row = plain.logits(ids)[-1]
+            want = plain_sample(row, greedy=False, temperature=0.7, u=uniform(sp.seed, i))
+            if t != want:       # only possible when u sits on the boundary between the two tokens
+                pr = torch.softmax(row.double() / 0.7, 0)
+                cdf = torch.cumsum(pr, 0)
+                assert abs(float(cdf[min(t, want)]) - uniform(sp.seed, i)) < 1e-4, (i, t, want)
+            ids.append(t)
+
+
+def test_top_k_top_p_and_penalty_through_the_entry_point(tmp_path):
+    d = make_model_dir(str(tmp_path / "m"), TINY_A, 9, dtype="bfloat16")
+    llm = LLM(d, dtype="float32", max_cached_tokens=512, max_num_seqs=2, max_num_batched_tokens=64)
+    plain = PlainQwen3(d)
+    p = random_ids(12, 512, 3)
+    sp = SamplingParams(greedy=False, temperature=1.3, top_k=5, top_p=0.9, repetition_penalty=1.2, seed=5)
+    toks = llm.generate(p, sp, max_tokens=12, eos_token_id=None)[0].token_ids
+    ids = list(p)
+    for i, t in enumerate(toks):
+        row = plain.logits(ids)[-1]
+        z = row.clone()
+        for h in ids:
+            z[h] = z[h] / 1.2 if z[h] > 0 else z[h] * 1.2
+        top5 = torch.topk(z, 5).indices.tolist()
+        assert t in top5, (i, t, top5)
+        ids.append(t)
+    greedy_pen = llm.generate(p, SamplingParams(repetition_penalty=1.2), max_tokens=8, eos_token_id=None)[0].token_ids
+    ids = list(p)
+    for t in greedy_pen:
+        want = plain_sample(plain.logits(ids)[-1], repetition_penalty=1.2, history=ids)
+        assert t == want
+        ids.append(t)
+
+
+def test_command_line(tmp_path):
+    d = make_model_dir(str(tmp_path / "m"), TINY_A, 5, dtype="bfloat16", sharpen=1.5)
+    p = subprocess.run([sys.executable, "-m", "llmengine_b200.generate", d, "5,17,3;9 8 7 6", "6", "--dtype", "float32",
+                        "--ignore-eos"], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l for l in p.stdout.splitlines() if l.strip()]
+    assert lines[-1] == "[Generated 12 tokens total]"
+    plain = PlainQwen3(d)
+    for prompt, line in zip(([5, 17, 3], [9, 8, 7, 6]), lines):
+        _check_greedy(plain, prompt, [int(x) for x in line.split()], 1e-4)

@@ -1,0 +1,315 @@
+"""Each part of a layer alone against the plain function of the same name, at sizes other than the
+engine tests use; and a toy mixer with state of its own, defined here, that is registered, built
+into a model and stepped without any change to the package."""
+import math
+
+import pytest
+import torch
+
+import plain_model as pm
+from llmengine_b200.config import ARCHITECTURES, EngineConfig, register_architecture
+from llmengine_b200.config.spec import LayerRun, LayerSpec, ModelSpec, PartSpec
+from llmengine_b200.engine.engine import Engine, StepEntry
+from llmengine_b200.parts import Part, Runtime, StateSpec, WeightSpec, build_part, register_part, registered
+from llmengine_b200.weights import random_tensor
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from llmengine_b200.kernels.ops import CudaOps
+    return CudaOps(torch.device(DEV))
+
+
+def _load_random(part, seed, dtype):
+    tensors = {}
+    for n, s in part.weight_specs().items():
+        t = random_tensor(n, s, seed)
+        tensors[n] = t.to(dtype if s.role == "matrix" else torch.float32).to(DEV)
+    part.load_weights(tensors)
+    return {n: t.float().cpu() for n, t in tensors.items()}
+
+
+# ----------------------------------------------------------------------------- parts alone (GPU)
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    rt = Runtime(_ops(), torch.device(DEV), dtype, 64)
+    norm = build_part("norm", PartSpec("rmsnorm", {"size": 200, "eps": 2e-5}), rt, "n")
+    w = _load_random(norm, 1, dtype)
+    x = torch.randn(11, 200, device=DEV)
+    delta = torch.randn(11, 200, device=DEV)
+    want = pm.rms_norm((x + delta).cpu(), w["n.weight"], 2e-5)
+    got = norm.forward(x, delta=delta)
+    assert got.dtype == dtype
+    assert (got.float().cpu() - want).abs().max() < (1e-5 if dtype == torch.float32 else 3e-2)
+
+
+@pytest.mark.gpu
+def test_position_part_table_matches_the_plain_rotation():
+    rt = Runtime(_ops(), torch.device(DEV), torch.float32, 64)
+    pe = build_part("position", PartSpec("rope", {"head_dim": 48, "theta": 77777.0, "max_positions": 300}), rt, "p")
+    q = torch.randn(9, 5 * 48, device=DEV)
+    k = torch.randn(9, 2 * 48, device=DEV)
+    pos = torch.tensor([0, 1, 2, 50, 51, 120, 250, 298, 299], dtype=torch.int32, device=DEV)
+    want_q = pm.rope(q.cpu().view(9, 5, 48), pos.cpu(), 77777.0).reshape(9, -1)
+    want_k = pm.rope(k.cpu().view(9, 2, 48), pos.cpu(), 77777.0).reshape(9, -1)
+    pe.apply(q, k, pos, 5, 2)                      # the unfused form, in place
+    assert (q.cpu() - want_q).abs().max() < 2e-5 and (k.cpu() - want_k).abs().max() < 2e-5
+    none = build_part("position", PartSpec("none"), rt, "p")
+    assert none.rotary_table() is None
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    rt = Runtime(_ops(), torch.device(DEV), dtype, 64)
+    ffn = build_part("feed_forward", PartSpec("swiglu", {"hidden_size": 72, "intermediate_size": 200}), rt, "f")
+    w = _load_random(ffn, 2, dtype)
+    h = torch.randn(13, 72, device=DEV).to(dtype)
+    hf = h.float().cpu()
+    want = pm.linear(pm.swiglu(pm.linear(hf, w["f.gate_proj.weight"]), pm.linear(hf, w["f.up_proj.weight"])),
+                     w["f.down_proj.weight"])
+    got = ffn.forward(h, None)
+    assert got.dtype == torch.float32
+    assert (got.cpu() - want).abs().max() < (1e-6 if dtype == torch.float32 else 2e-4)
+
+
+@pytest.mark.gpu
+def test_embedding_and_head_parts():
+    rt = Runtime(_ops(), torch.device(DEV), torch.float32, 64)
+    emb = build_part("embedding", PartSpec("token_embedding", {"vocab_size": 333, "hidden_size": 40}), rt, "e")
+    w = _load_random(emb, 3, torch.float32)
+    ids = torch.tensor([0, 332, 17, 17], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids).cpu(), pm.embedding(w["e.weight"], ids.tolist()))
+    head = build_part("head", PartSpec("lm_head", {"vocab_size": 333, "hidden_size": 40, "tied": True}), rt, "h")
+    assert head.weight_specs() == {}
+    head.tie(emb.table)
+    h = torch.randn(3, 40, device=DEV)
+    assert (head.forward(h).cpu() - pm.linear(h.cpu(), w["e.weight"])).abs().max() < 1e-5
+
+
+def _one_layer_engine(tmp_path, dtype, **mixer_over):
+    from helpers import make_model_dir
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 1, "hidden_size": 56, "num_attention_heads": 6,
+           "num_key_value_heads": 2, "head_dim": 32, "intermediate_size": 88, "vocab_size": 301, "rope_theta": 3000.0,
+           "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 128, "hidden_act": "silu"}
+    d = make_model_dir(str(tmp_path / "one"), cfg, 4, dtype="bfloat16", sharpen=2.0)
+    ec = EngineConfig(dtype=dtype, page_size=4, max_cached_tokens=128, max_num_seqs=4, max_num_batched_tokens=128,
+                      use_cuda_graphs=False)
+    return Engine(d, engine_config=ec), pm.PlainQwen3(d, round_to=torch.bfloat16 if dtype == "bfloat16" else None), cfg
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixer_part_alone_over_two_steps(tmp_path, dtype):
+    """The attention part's forward on hand-made inputs: a first portion, then a second one that must
+    find the first one's keys in the cache."""
+    eng, plain, cfg = _one_layer_engine(tmp_path, dtype)
+    mixer = eng.model.blocks[0].mixer
+    T1, T2, H = 21, 10, cfg["hidden_size"]
+    h_all = torch.randn(T1 + T2, H).to(eng.dtype)
+    hf = h_all.float()
+    w = plain.w
+    p = "model.layers.0.self_attn."
+    rt = plain.round_to
+    r = (lambda x: x.to(rt).float()) if rt else (lambda x: x)
+    nh, nkv, hd = 6, 2, 32
+    pos = torch.arange(T1 + T2)
+    q = r(pm.rope(pm.qk_norm(r(pm.linear(hf, w[p + "q_proj.weight"])).view(-1, nh, hd), w[p + "q_norm.weight"], 1e-5), pos, 3000.0))
+    k = r(pm.rope(pm.qk_norm(r(pm.linear(hf, w[p + "k_proj.weight"])).view(-1, nkv, hd), w[p + "k_norm.weight"], 1e-5), pos, 3000.0))
+    v = r(pm.linear(hf, w[p + "v_proj.weight"])).view(-1, nkv, hd)
+    want = pm.linear(r(pm.attention(q, k, v).reshape(-1, nh * hd)), w[p + "o_proj.weight"])
+    got = []
+    for start, n in ((0, T1), (T1, T2)):
+        eng.cache.has("x") or eng.cache.add_request("x")
+        eng.cache.reserve("x", start + n)
+        batch = eng._build_batch([StepEntry("x", [0] * n, [])], [start])
+        eng.cache.flush()
+        got.append(mixer.forward(h_all[start:start + n].to(DEV).contiguous(), batch, eng._caches[0]).cpu().clone())
+        eng.cache.advance("x", start + n)
+        eng.steps += 1
+    got = torch.cat(got)
+    assert (got - want).abs().max() < (2e-5 if dtype == "float32" else 2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_part_alone(tmp_path, dtype):
+    eng, plain, cfg = _one_layer_engine(tmp_path, dtype)
+    block = eng.model.blocks[0]
+    T, H = 17, cfg["hidden_size"]
+    x0 = torch.randn(T, H)
+    d0 = torch.randn(T, H) * 0.1
+    # plain: one layer body on x = x0 + d0
+    rt = plain.round_to
+    r = (lambda t: t.to(rt).float()) if rt else (lambda t: t)
+    w, p = plain.w, "model.layers.0."
+    x = x0 + d0
+    h = r(pm.rms_norm(x, w[p + "input_layernorm.weight"], 1e-5))
+    pos = torch.arange(T)
+    q = r(pm.rope(pm.qk_norm(r(pm.linear(h, w[p + "self_attn.q_proj.weight"])).view(T, 6, 32), w[p + "self_attn.q_norm.weight"], 1e-5), pos, 3000.0))
+    k = r(pm.rope(pm.qk_norm(r(pm.linear(h, w[p + "self_attn.k_proj.weight"])).view(T, 2, 32), w[p + "self_attn.k_norm.weight"], 1e-5), pos, 3000.0))
+    v = r(pm.linear(h, w[p + "self_attn.v_proj.weight"])).view(T, 2, 32)
+    x = pm.linear(r(pm.attention(q, k, v).reshape(T, -1)), w[p + "self_attn.o_proj.weight"]) + x
+    h = r(pm.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-5))
+    f = pm.linear(r(pm.swiglu(r(pm.linear(h, w[p + "mlp.gate_proj.weight"])), r(pm.linear(h, w[p + "mlp.up_proj.weight"])))),
+                  w[p + "mlp.down_proj.weight"])
+    eng.cache.add_request("x")
+    eng.cache.reserve("x", T)
+    batch = eng._build_batch([StepEntry("x", [0] * T, [])], [0])
+    eng.cache.flush()
+    xg, dg = block.forward(x0.to(DEV), d0.to(DEV), batch, eng._caches[0])
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    assert (xg.cpu() - x).abs().max() < tol, "the residual stream after the mixer"
+    assert (dg.cpu() - f).abs().max() < tol, "the feed-forward's contribution, not yet added"
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state
+@register_part("mixer", "toy_decaying_sum")
+class ToyDecayingSum(Part):
+    """y_t = W s_t with s_t = decay * s_{t-1} + h_t: a state of fixed size per request, carried from
+    one portion to the next through the request's state slot.  Written with plain tensor operations;
+    it exists only to show that a mixer of another kind plugs in."""
+
+    def __init__(self, rt, prefix, hidden_size, decay):
+        super().__init__(rt, prefix)
+        self.hidden, self.decay = hidden_size, decay
+        self.w = None
+
+    def weight_specs(self):
+        return {self.name("mix.weight"): WeightSpec((self.hidden, self.hidden))}
+
+    def load_weights(self, t):
+        self.w = t[self.name("mix.weight")].float()
+
+    def cache_spec(self):
+        return StateSpec((self.hidden,), torch.float32)
+
+    def forward(self, h, batch, cache):
+        out = torch.empty(h.shape[0], self.hidden, dtype=torch.float32, device=h.device)
+        slots = batch.state_slots.tolist()
+        a = 0
+        for r, n in enumerate(batch.q_lens):                 # a request's portion is processed in order
+            s = cache.state[slots[r]]
+            if batch.start_positions[r] == 0:
+                assert float(s.abs().max()) == 0.0, "a new request must find a zeroed state"
+            for t in range(a, a + n):
+                s = self.decay * s + h[t].float()
+                out[t] = self.w @ s
+            cache.state[slots[r]] = s
+            a += n
+        return out
+
+
+class ToyConfig:
+    """An architecture made of the toy mixer and the package's other parts."""
+
+    ARCHITECTURE = "ToyStateForCausalLM"
+
+    def __init__(self, d):
+        self.d = dict(d)
+        self.vocab_size, self.hidden_size = d["vocab_size"], d["hidden_size"]
+        self.tie_word_embeddings = False
+        self.eos_token_id = None
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def to_dict(self):
+        return dict(self.d)
+
+    @staticmethod
+    def canonical_tensor_name(n):
+        return n
+
+    def model_spec(self):
+        H, d = self.hidden_size, self.d
+        norm = PartSpec("rmsnorm", {"size": H, "eps": d["eps"]})
+        attn = PartSpec("gqa_attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 1, "head_dim": 16,
+                                          "qk_norm_eps": None, "window": 0, "position_encoding": PartSpec("none")})
+        toy = PartSpec("toy_decaying_sum", {"hidden_size": H, "decay": d["decay"]})
+        ffn = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": d["inter"]})
+        layers = tuple(LayerSpec(f"layers.{i}", PartSpec("prenorm_residual"), m, norm, ffn, norm)
+                       for i, m in enumerate((toy, attn, toy)))
+        return ModelSpec(self.ARCHITECTURE, H, self.vocab_size, d["max_positions"],
+                         PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": H}), layers,
+                         tuple(LayerRun(i) for i in range(3)), norm,
+                         PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": H}))
+
+
+if ToyConfig.ARCHITECTURE not in ARCHITECTURES:
+    register_architecture(ToyConfig.ARCHITECTURE, ToyConfig)
+
+TOY = {"architectures": [ToyConfig.ARCHITECTURE], "vocab_size": 97, "hidden_size": 40, "inter": 72, "eps": 1e-5,
+       "decay": 0.9, "max_positions": 256}
+
+
+def _plain_toy(eng, ids):
+    """Whole-sequence evaluation of the toy model from the engine's loaded tensors, with plain functions."""
+    m = eng.model
+    f = lambda t: t.float().cpu()
+    x = pm.embedding(f(m.embedding.table), ids)
+    T = len(ids)
+    for blk in m.blocks:
+        h = pm.rms_norm(x, f(blk.mixer_norm.gain), blk.mixer_norm.eps)
+        if isinstance(blk.mixer, ToyDecayingSum):
+            s = torch.zeros(h.shape[1])
+            rows = []
+            for t in range(T):
+                s = 0.9 * s + h[t]
+                rows.append(f(blk.mixer.w) @ s)
+            a = torch.stack(rows)
+        else:
+            mx = blk.mixer
+            qkv = pm.linear(h, f(mx.w_qkv))
+            q = qkv[:, :mx.q_size].view(T, mx.nh, mx.hd)
+            k = qkv[:, mx.q_size:mx.q_size + mx.kv_size].view(T, mx.nkv, mx.hd)
+            v = qkv[:, mx.q_size + mx.kv_size:].view(T, mx.nkv, mx.hd)
+            a = pm.linear(pm.attention(q, k, v).reshape(T, -1), f(mx.w_o))
+        x = x + a
+        h = pm.rms_norm(x, f(blk.ffn_norm.gain), blk.ffn_norm.eps)
+        gu = pm.linear(h, f(blk.ffn.w_gate_up))
+        x = x + pm.linear(pm.swiglu(gu[:, :blk.ffn.inter], gu[:, blk.ffn.inter:]), f(blk.ffn.w_down))
+    return pm.linear(pm.rms_norm(x, f(m.final_norm.gain), m.final_norm.eps), f(m.head.weight))
+
+
+def _toy_roundtrip(ops, device):
+    assert "toy_decaying_sum" in registered("mixer")
+    ec = EngineConfig(dtype="float32", page_size=8, max_cached_tokens=256, max_num_seqs=3, max_num_batched_tokens=128,
+                      device=device, use_cuda_graphs=False)
+    eng = Engine(config=TOY, random_seed=5, engine_config=ec, ops=ops)
+    assert [type(s).__name__ for s, _ in eng.model.cache_specs()] == ["StateSpec", "PagedKVSpec", "StateSpec"]
+    from helpers import random_ids
+    a, b = random_ids(50, 97, 1), random_ids(31, 97, 2)
+    want_a, want_b = _plain_toy(eng, a), _plain_toy(eng, b)
+    # whole
+    got = eng.step([StepEntry("a", a, range(50))], end=["a"]).cpu()
+    assert (got - want_a).abs().max() < 1e-4
+    # portions of a beside b, b starting later and decoding one by one at the end; then a slot is used again
+    rows_a, rows_b = [], []
+    sched = [(("a", 0, 20),), (("a", 20, 2), ("b", 0, 17)), (("b", 17, 13), ("a", 22, 27)), (("a", 49, 1), ("b", 30, 1))]
+    for step in sched:
+        entries = [StepEntry(r, (a if r == "a" else b)[s:s + n], range(n)) for r, s, n in step]
+        out = eng.step(entries).cpu()
+        o = 0
+        for r, s, n in step:
+            (rows_a if r == "a" else rows_b).append(out[o:o + n].clone())
+            o += n
+    assert (torch.cat(rows_a) - want_a).abs().max() < 1e-4
+    assert (torch.cat(rows_b) - want_b).abs().max() < 1e-4
+    eng.free("a"), eng.free("b")
+    got = eng.step([StepEntry("c", b, range(31))], end=["c"]).cpu()      # finds its slot's state zeroed again
+    assert (got - want_b).abs().max() < 1e-4
+    eng.cache.check_invariants()
+
+
+def test_toy_stateful_mixer_on_the_host():
+    from host_ops import HostOps
+    _toy_roundtrip(HostOps(), "cpu")
+
+
+@pytest.mark.gpu
+def test_toy_stateful_mixer_registers_builds_and_steps():
+    _toy_roundtrip(None, DEV)
