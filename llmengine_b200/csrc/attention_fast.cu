@@ -7,8 +7,9 @@
 //                             scores and the running softmax stay in registers, 32-bit.
 //   attention_decode_kernel   one new token per request: the query heads of one key/value head
 //                             form the (padded) 16-row tile, the context is split over blocks and
-//                             over the four warps of a block, partial (max, sum, output) triples go
-//                             to scratch memory and attention_combine_kernel merges them.
+//                             over the four warps of a block (each warp streams its own 16-key
+//                             sub-tiles), partial (max, sum, output) triples go to scratch memory
+//                             and attention_combine_kernel merges them.
 //
 // Both read keys and values only from the cache pages through the block table, mask by the
 // absolute position of each query (causal, optional window) and never let a cache row outside
@@ -306,16 +307,45 @@ __global__ void __launch_bounds__(THREADS) attention_portion_kernel(FastAttnArgs
 }
 
 // ----------------------------------------------------------------------------- decode
-// grid (splits, nkv * head_chunks, n_rows).  Scratch per (request row, query head, split): HD outputs
-// (not normalised), then max (base-2 units) and sum.
+// grid (splits, nkv * head_chunks, n_rows).  A block serves one request, one key/value head (up to 16 of
+// its query heads) and one share of the context.  Its four warps work independently: warp w takes the
+// 16-key sub-tiles w, w+4, w+8, ... of the block's share and streams them through a pipeline of its own
+// (DSTAGES sub-tiles in flight per warp, no block-wide barrier inside the loop), so that enough bytes are
+// in flight to cover the memory latency.  At the end the warps' partial results are merged in shared
+// memory; with more than one split the block's result goes to scratch memory.
+// Scratch per (request row, query head, split): HD outputs (not normalised), then max (base-2 units) and sum.
 constexpr int PART = HD + 2;
+constexpr int SUB = 16;           // keys per sub-tile
+constexpr int DSTAGES = 3;        // stage buffers per warp (two sub-tiles in flight while one is used); two blocks fit an SM
+constexpr int STAGE_ELEMS = 2 * SUB * LDS;   // K rows then V rows
+
+// One warp loads keys [j0, j0+16) (K and V) into its stage buffer; keys outside [lo, hi] become zeros.
+__device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, const int* bt, int kvh, int nkv, int ps,
+                                              int page_shift, int j0, int lo, int hi) {
+    const int lane = threadIdx.x & 31;
+    constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per key row
+    constexpr int TOTAL = SUB * CHUNKS;            // chunks of K (and as many of V)
+#pragma unroll
+    for (int c = lane; c < TOTAL; c += 32) {
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        const int j = j0 + r;
+        const bool valid = j >= lo && j <= hi;
+        const bf16* ksrc = cache;
+        if (valid) {
+            const int blk = page_shift >= 0 ? (j >> page_shift) : (j / ps);
+            const int page = bt[blk];
+            ksrc = cache + ((((size_t)page * 2) * nkv + kvh) * ps + (j - blk * ps)) * HD + ch * 8;
+        }
+        cp_async_16(dst + r * LDS + ch * 8, ksrc, valid);
+        cp_async_16(dst + (SUB + r) * LDS + ch * 8, valid ? ksrc + (size_t)nkv * ps * HD : cache, valid);
+    }
+}
 
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][LDS]
-    bf16* Ks = Qs + 16 * LDS;                              // [2][BN][LDS]
-    bf16* Vs = Ks + 2 * BN * LDS;                          // [2][BN][LDS]
-    float* red = reinterpret_cast<float*>(Ks);              // [4 warps][16 rows][PART], reuses the key tiles after the loop
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][LDS]
+    bf16* stages = Qs + 16 * LDS;                              // [4 warps][DSTAGES][K 16 rows | V 16 rows][LDS]
+    float* red = reinterpret_cast<float*>(stages);             // [4 warps][16 rows][PART], reuses the stages after the loop
 
     const int zi = blockIdx.z;
     const int r = a.rows[zi];
@@ -329,13 +359,15 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
     const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
     const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ps = a.page_size;
+    const int page_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
 
-    // this block's share of the key tiles
-    const int tile_first = lo / BN, tile_last = p / BN;
-    const int n_tiles = tile_last - tile_first + 1;
-    const int per = (n_tiles + a.splits - 1) / a.splits;
-    const int my_first = tile_first + split * per;
-    const int my_last = min(tile_last, my_first + per - 1);
+    // this block's share of the 16-key sub-tiles, in whole groups of four (one per warp)
+    const int sub_first = lo / SUB, sub_last = p / SUB;
+    const int n_groups = (sub_last - sub_first + 4) / 4;
+    const int per = (n_groups + a.splits - 1) / a.splits;
+    const int my_first = sub_first + split * per * 4;
+    const int my_last = min(sub_last, my_first + per * 4 - 1);
 
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     float o[DTILES][4];
@@ -343,6 +375,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
 
     if (my_first <= my_last) {
+        // the query rows, loaded by the whole block
         {
             constexpr int CHUNKS = HD / 8;
             for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
@@ -352,44 +385,46 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
                 if (valid) src = a.q + ((size_t)t * a.nh + kvh * G + g0 + row) * HD + ch * 8;
                 cp_async_16(Qs + row * LDS + ch * 8, src, valid);
             }
+            cp_async_commit();
         }
-        load_kv_tile(Ks, a.cache, bt, 0, kvh, a.nkv, a.page_size, my_first * BN, lo, p);
-        load_kv_tile(Vs, a.cache, bt, 1, kvh, a.nkv, a.page_size, my_first * BN, lo, p);
-        cp_async_commit();
+        bf16* mine = stages + (size_t)warp * DSTAGES * STAGE_ELEMS;
+        // prologue: the first DSTAGES-1 sub-tiles of this warp
+#pragma unroll
+        for (int st = 0; st < DSTAGES - 1; ++st) {
+            const int sub = my_first + warp + 4 * st;
+            if (sub <= my_last) load_sub_tile(mine + st * STAGE_ELEMS, a.cache, bt, kvh, a.nkv, ps, page_shift, sub * SUB, lo, p);
+            cp_async_commit();
+        }
+        cp_async_wait<DSTAGES - 1>();                       // the query rows have landed
+        __syncthreads();
+        unsigned qf[KSTEPS][4];
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk)
+            ldmatrix_x4(qf[kk], Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 16 + (lane >> 4) * 8);
+
         int plo[2] = {lo, lo}, phi[2];
         phi[0] = (lane >> 2) < rows_here ? p : -1;
         phi[1] = (lane >> 2) + 8 < rows_here ? p : -1;
-        unsigned qf[KSTEPS][4];
         const float sc = a.scale * LOG2E;
-        int buf = 0;
-        for (int tile = my_first; tile <= my_last; ++tile) {
-            if (tile + 1 <= my_last) {
-                load_kv_tile(Ks + (buf ^ 1) * BN * LDS, a.cache, bt, 0, kvh, a.nkv, a.page_size, (tile + 1) * BN, lo, p);
-                load_kv_tile(Vs + (buf ^ 1) * BN * LDS, a.cache, bt, 1, kvh, a.nkv, a.page_size, (tile + 1) * BN, lo, p);
-            }
+        int n = 0;
+        for (int sub = my_first + warp; sub <= my_last; sub += 4, ++n) {
+            const int ahead = sub + 4 * (DSTAGES - 1);
+            if (ahead <= my_last)
+                load_sub_tile(mine + ((n + DSTAGES - 1) % DSTAGES) * STAGE_ELEMS, a.cache, bt, kvh, a.nkv, ps, page_shift,
+                              ahead * SUB, lo, p);
             cp_async_commit();
-            cp_async_wait<1>();
-            __syncthreads();
-            if (tile == my_first) {
+            cp_async_wait<DSTAGES - 1>();                   // this lane's copies of sub-tile n are done
+            __syncwarp();                                   // ... and so are the other lanes'
+            const bf16* Kt = mine + (n % DSTAGES) * STAGE_ELEMS;
+            float sreg[2][4];
+            qk_tile<2>(sreg, qf, Kt, 0);
 #pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk)
-                    ldmatrix_x4(qf[kk], Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 16 + (lane >> 4) * 8);
-            }
-            // each warp takes 16 of the tile's 64 keys
-            const int key0 = warp * 16;
-            const int jbase = tile * BN + key0;
-            if (jbase <= p && jbase + 15 >= lo) {
-                float s[2][4];
-                qk_tile<2>(s, qf, Ks + buf * BN * LDS, key0);
+            for (int i = 0; i < 2; ++i)
 #pragma unroll
-                for (int n = 0; n < 2; ++n)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) s[n][c] *= sc;
-                softmax_update<2>(s, m_run, l_run, o, jbase, plo, phi);
-                pv_tile<2>(o, s, Vs + buf * BN * LDS, key0);
-            }
-            __syncthreads();
-            buf ^= 1;
+                for (int c = 0; c < 4; ++c) sreg[i][c] *= sc;
+            softmax_update<2>(sreg, m_run, l_run, o, sub * SUB, plo, phi);
+            pv_tile<2>(o, sreg, Kt + SUB * LDS, 0);
+            __syncwarp();                                   // all lanes have read the stage before it is refilled
         }
         cp_async_wait<0>();
     }
@@ -449,7 +484,9 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
     }
 }
 
-// One warp per (request row, query head): merge the splits' partial results.
+// One warp per (request row, query head): merge the splits' partial results.  The lanes first take one
+// split each (maximum and total weight), then one output column each; the loads of a loop do not depend
+// on each other, so they are in flight together.
 __global__ void attention_combine_kernel(FastAttnArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int idx = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -459,25 +496,35 @@ __global__ void attention_combine_kernel(FastAttnArgs a) {
     const int t = a.cu_q_lens[r];
     const float* src = a.scratch + (size_t)idx * a.splits * PART;
     float mm = -INFINITY;
-    for (int s = 0; s < a.splits; ++s) mm = fmaxf(mm, src[s * PART + HD]);
+    for (int s = lane; s < a.splits; s += 32) mm = fmaxf(mm, src[s * PART + HD]);
+    mm = warp_max(mm);
     const float ref = mm == -INFINITY ? 0.0f : mm;
     float ll = 0.0f;
-    for (int s = 0; s < a.splits; ++s) ll += exp2f(src[s * PART + HD] - ref) * src[s * PART + HD + 1];
+    for (int s = lane; s < a.splits; s += 32) ll += exp2f(src[s * PART + HD] - ref) * src[s * PART + HD + 1];
+    ll = warp_sum(ll);
     const float inv = 1.0f / ll;
     bf16* dst = a.out + ((size_t)t * a.nh + head) * HD;
-    for (int d = lane; d < HD; d += 32) {
-        float acc = 0.0f;
-        for (int s = 0; s < a.splits; ++s) {
-            const float w = exp2f(src[s * PART + HD] - ref);
-            if (w != 0.0f) acc += w * src[s * PART + d];     // an empty split holds zeros and weight 0
+    float acc[(HD + 31) / 32];
+#pragma unroll
+    for (int k = 0; k < (HD + 31) / 32; ++k) acc[k] = 0.0f;
+    for (int s = 0; s < a.splits; ++s) {
+        const float w = exp2f(src[s * PART + HD] - ref);
+#pragma unroll
+        for (int k = 0; k < (HD + 31) / 32; ++k) {
+            const int d = lane + 32 * k;
+            if (d < HD && w != 0.0f) acc[k] += w * src[s * PART + d];      // an empty split holds zeros and weight 0
         }
-        dst[d] = __float2bfloat16_rn(acc * inv);
+    }
+#pragma unroll
+    for (int k = 0; k < (HD + 31) / 32; ++k) {
+        const int d = lane + 32 * k;
+        if (d < HD) dst[d] = __float2bfloat16_rn(acc[k] * inv);
     }
 }
 
 constexpr size_t PORTION_SMEM = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
-constexpr size_t DECODE_SMEM = (size_t)(16 + 4 * BN) * LDS * sizeof(bf16);
-static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)2 * BN * LDS * sizeof(bf16), "the merge buffer must fit the key tiles");
+constexpr size_t DECODE_SMEM = (size_t)(16 * LDS + 4 * DSTAGES * STAGE_ELEMS) * sizeof(bf16);
+static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)4 * DSTAGES * STAGE_ELEMS * sizeof(bf16), "the merge buffer must fit the stage buffers");
 
 int check_common(const FastAttnArgs& a) {
     if (!a.q || !a.cache || !a.out || !a.rows || !a.cu_q_lens || !a.ctx_lens || !a.table_rows || !a.block_tables)

@@ -27,11 +27,38 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const W* __restric
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = to_f32(row[j]);
 }
 
+// The same for bfloat16 tables whose rows are a multiple of 8 wide: 16 bytes in, 32 bytes out per thread.
+__global__ void embedding_bf16x8_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                        float* __restrict__ out, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)(ok ? id : 0) * hidden);
+    float4* o = reinterpret_cast<float4*>(out + (size_t)t * hidden);
+    for (int j = threadIdx.x; j < hidden / 8; j += blockDim.x) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (ok) {
+            const uint4 v = row[j];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+            const float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
+            a = make_float4(f0.x, f0.y, f1.x, f1.y);
+            b = make_float4(f2.x, f2.y, f3.x, f3.y);
+        }
+        o[2 * j] = a;
+        o[2 * j + 1] = b;
+    }
+}
+
 LLME_API int llme_embedding(const int* ids, const void* table, int table_dtype, float* out,
                             int tokens, int hidden, int vocab, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (!ids || !table || !out || hidden <= 0 || vocab <= 0) LLME_REFUSE("embedding: null pointer or non-positive size");
     const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == LLME_BF16 && hidden % 8 == 0 && ((uintptr_t)table % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        embedding_bf16x8_kernel<<<tokens, hidden >= 2048 ? 256 : 64, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+        LLME_LAUNCH_STATUS();
+    }
     if (table_dtype == LLME_F32)
         embedding_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
     else if (table_dtype == LLME_BF16)
@@ -71,9 +98,90 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const D* __restrict__ delt
     }
 }
 
+// Vector form for rows that are a multiple of 4 wide: each thread keeps up to V groups of 4 values of the
+// row in registers, so the row is read once, and all its loads are in flight together.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        uint2 raw;
+        *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename D, typename G, typename O, bool HAS_DELTA, int V>
+__global__ void rmsnorm_vec_kernel(float* __restrict__ x, const D* __restrict__ delta, const G* __restrict__ gain,
+                                   O* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* xr = x + (size_t)r * hidden;
+    const int groups = hidden >> 2;
+    float4 v[V], g[V];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j < groups) {
+            v[k] = Vec4<float>::load(xr + 4 * j);
+            g[k] = Vec4<G>::load(gain + 4 * j);
+            if (HAS_DELTA) {
+                const float4 d = Vec4<D>::load(delta + (size_t)r * hidden + 4 * j);
+                v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j < groups) {
+            if (HAS_DELTA) Vec4<float>::store(xr + 4 * j, v[k]);
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    O* o = out + (size_t)i * hidden;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        const int j = threadIdx.x + k * blockDim.x;
+        if (j < groups)
+            Vec4<O>::store(o + 4 * j, make_float4((v[k].x * rinv) * g[k].x, (v[k].y * rinv) * g[k].y,
+                                                  (v[k].z * rinv) * g[k].z, (v[k].w * rinv) * g[k].w));
+    }
+}
+
+template <typename D, typename G, typename O, bool HAS_DELTA>
+static bool launch_rmsnorm_vec(float* x, const void* delta, const void* gain, void* out, const int* rows,
+                               int n_out, int hidden, float eps, cudaStream_t s) {
+    if (hidden % 4 || hidden > 16384) return false;
+    if (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)out) % 16) return false;
+    const int groups = hidden / 4;
+    // few rows: short dependency chains matter more than occupancy, so spread the row over many threads
+    if (groups <= 256)
+        rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 1><<<n_out, ((groups + 31) / 32) * 32, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+    else if (groups <= 1024)
+        rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 2><<<n_out, (((groups + 1) / 2 + 31) / 32) * 32, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+    else
+        rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 4><<<n_out, (((groups + 3) / 4 + 31) / 32) * 32, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+    return true;
+}
+
 template <typename D, typename G, typename O, bool HAS_DELTA>
 static void launch_rmsnorm(float* x, const void* delta, const void* gain, void* out, const int* rows,
                            int n_out, int hidden, float eps, cudaStream_t s) {
+    if (launch_rmsnorm_vec<D, G, O, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s)) return;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     rmsnorm_kernel<D, G, O, HAS_DELTA><<<n_out, threads, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
 }
@@ -205,12 +313,145 @@ __global__ void qkv_post_kernel(QkvArgs a) {
     }
 }
 
+// Vector form for head sizes that are a multiple of 4: a lane holds two neighbouring values of the
+// first half of the head and the two values they are paired with in the second half, for up to NP such
+// groups; the head is read once (4- or 8-byte loads) and stays in registers through norm and rotation.
+template <typename T> struct Vec2;
+template <> struct Vec2<float> {
+    static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+    static __device__ __forceinline__ void store(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+};
+template <> struct Vec2<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 v) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y); }
+};
+
+template <typename I, typename O, typename G, int NP>
+__global__ void qkv_post_vec_kernel(QkvArgs a) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int heads = a.nh + 2 * a.nkv;
+    if (wid >= (long long)a.tokens * heads) return;
+    const int t = (int)(wid / heads);
+    const int h = (int)(wid % heads);
+    const int hd = a.hd, half = hd >> 1;
+
+    if (h >= a.nh + a.nkv) {                       // value head: copy into the cache
+        if (!a.cache || !a.v_in) return;
+        const int slot = a.slot_mapping[t];
+        if (slot < 0) return;
+        const int kvh = h - a.nh - a.nkv;
+        const I* src = (const I*)a.v_in + (size_t)t * a.v_stride + (size_t)kvh * hd;
+        const int page = slot / a.page_size, off = slot % a.page_size;
+        O* dst = (O*)a.cache + ((((size_t)page * 2 + 1) * a.nkv + kvh) * a.page_size + off) * hd;
+#pragma unroll
+        for (int i = 0; i < 2 * NP; ++i) {
+            const int d = 2 * (lane + 32 * i);
+            if (d < hd) Vec2<O>::store(dst + d, Vec2<I>::load(src + d));
+        }
+        return;
+    }
+
+    const bool is_q = h < a.nh;
+    const int head = is_q ? h : h - a.nh;
+    const I* src;
+    if (is_q) {
+        if (!a.q_in) return;
+        src = (const I*)a.q_in + (size_t)t * a.q_stride + (size_t)head * hd;
+    } else {
+        if (!a.k_in) return;
+        src = (const I*)a.k_in + (size_t)t * a.k_stride + (size_t)head * hd;
+    }
+    const G* gain = (const G*)(is_q ? a.q_gain : a.k_gain);
+
+    float2 lo[NP], hi[NP];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+        const int d = 2 * (lane + 32 * i);
+        if (d < half) {
+            lo[i] = Vec2<I>::load(src + d);
+            hi[i] = Vec2<I>::load(src + d + half);
+            ss += lo[i].x * lo[i].x + lo[i].y * lo[i].y + hi[i].x * hi[i].x + hi[i].y * hi[i].y;
+        }
+    }
+    if (gain) {
+        ss = warp_sum(ss);
+        const float rinv = 1.0f / sqrtf(ss / (float)hd + a.eps);
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const int d = 2 * (lane + 32 * i);
+            if (d < half) {
+                const float2 g0 = Vec2<G>::load(gain + d), g1 = Vec2<G>::load(gain + d + half);
+                lo[i].x = (lo[i].x * rinv) * g0.x; lo[i].y = (lo[i].y * rinv) * g0.y;
+                hi[i].x = (hi[i].x * rinv) * g1.x; hi[i].y = (hi[i].y * rinv) * g1.y;
+            }
+        }
+    }
+    if (a.cos_sin) {
+        int pos = a.positions[t];
+        pos = pos < 0 ? 0 : (pos >= a.max_positions ? a.max_positions - 1 : pos);   // the host refuses such positions
+        const float* cs = a.cos_sin + (size_t)pos * hd;
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const int d = 2 * (lane + 32 * i);
+            if (d < half) {
+                const float2 c = *reinterpret_cast<const float2*>(cs + d);
+                const float2 s = *reinterpret_cast<const float2*>(cs + half + d);
+                const float2 x0 = lo[i], x1 = hi[i];
+                lo[i] = make_float2(x0.x * c.x - x1.x * s.x, x0.y * c.y - x1.y * s.y);
+                hi[i] = make_float2(x0.x * s.x + x1.x * c.x, x0.y * s.y + x1.y * c.y);
+            }
+        }
+    }
+    O* q_dst = (is_q && a.q_out) ? (O*)a.q_out + ((size_t)t * a.nh + head) * hd : nullptr;
+    O* k_dst = (!is_q && a.k_out) ? (O*)a.k_out + ((size_t)t * a.nkv + head) * hd : nullptr;
+    O* c_dst = nullptr;
+    if (!is_q && a.cache) {
+        const int slot = a.slot_mapping[t];
+        if (slot >= 0) {
+            const int page = slot / a.page_size, off = slot % a.page_size;
+            c_dst = (O*)a.cache + ((((size_t)page * 2 + 0) * a.nkv + head) * a.page_size + off) * hd;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+        const int d = 2 * (lane + 32 * i);
+        if (d < half) {
+            if (q_dst) { Vec2<O>::store(q_dst + d, lo[i]); Vec2<O>::store(q_dst + d + half, hi[i]); }
+            if (k_dst) { Vec2<O>::store(k_dst + d, lo[i]); Vec2<O>::store(k_dst + d + half, hi[i]); }
+            if (c_dst) { Vec2<O>::store(c_dst + d, lo[i]); Vec2<O>::store(c_dst + d + half, hi[i]); }
+        }
+    }
+}
+
+template <typename I, typename O, typename G>
+static bool launch_qkv_vec(const QkvArgs& a, unsigned blocks, int threads, cudaStream_t s) {
+    if (a.hd % 4 || a.hd > 512) return false;
+    if ((a.q_stride | a.k_stride | a.v_stride) & 1) return false;
+    const uintptr_t ptrs = (uintptr_t)a.q_in | (uintptr_t)a.k_in | (uintptr_t)a.v_in | (uintptr_t)a.q_gain |
+                           (uintptr_t)a.k_gain | (uintptr_t)a.cos_sin | (uintptr_t)a.q_out | (uintptr_t)a.k_out |
+                           (uintptr_t)a.cache;
+    if (ptrs % 8) return false;
+    const int half = a.hd / 2;
+    if (half <= 64) qkv_post_vec_kernel<I, O, G, 1><<<blocks, threads, 0, s>>>(a);
+    else if (half <= 128) qkv_post_vec_kernel<I, O, G, 2><<<blocks, threads, 0, s>>>(a);
+    else qkv_post_vec_kernel<I, O, G, 4><<<blocks, threads, 0, s>>>(a);
+    return true;
+}
+
 template <typename I, typename O>
 static int dispatch_qkv_gain(const QkvArgs& a, cudaStream_t s) {
     const long long warps = (long long)a.tokens * (a.nh + 2 * a.nkv);
     const int wpb = 8;
     const long long blocks = (warps + wpb - 1) / wpb;
     if (blocks > 2147483647LL) LLME_REFUSE("qkv_post: too many (token, head) pairs for one launch");
+    if (a.gain_dtype == LLME_F32 || !(a.q_gain || a.k_gain)) {
+        if (launch_qkv_vec<I, O, float>(a, (unsigned)blocks, wpb * 32, s)) LLME_LAUNCH_STATUS();
+    } else if (a.gain_dtype == LLME_BF16) {
+        if (launch_qkv_vec<I, O, __nv_bfloat16>(a, (unsigned)blocks, wpb * 32, s)) LLME_LAUNCH_STATUS();
+    }
     if (a.gain_dtype == LLME_F32) qkv_post_kernel<I, O, float><<<(unsigned)blocks, wpb * 32, 0, s>>>(a);
     else if (a.gain_dtype == LLME_BF16) qkv_post_kernel<I, O, __nv_bfloat16><<<(unsigned)blocks, wpb * 32, 0, s>>>(a);
     else LLME_REFUSE("qkv_post: unsupported gain dtype %d", a.gain_dtype);
@@ -246,10 +487,36 @@ __global__ void swiglu_kernel(const I* __restrict__ in, O* __restrict__ out, lon
     }
 }
 
+// Vector form: 8 values per thread (two 16-byte loads, one 16-byte store for bfloat16), grid (column chunks, tokens).
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int inter) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= inter) return;
+    const size_t t = blockIdx.y;
+    const uint4 gv = *reinterpret_cast<const uint4*>(in + t * 2 * inter + c);
+    const uint4 uv = *reinterpret_cast<const uint4*>(in + t * 2 * inter + inter + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+        o2[k] = __floats2bfloat162_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * inter + c) = ov;
+}
+
 LLME_API int llme_swiglu(const void* in, int in_dtype, void* out, int out_dtype, int tokens, int inter,
                          cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (!in || !out || inter <= 0) LLME_REFUSE("swiglu: null pointer or non-positive size");
+    if (in_dtype == LLME_BF16 && out_dtype == LLME_BF16 && inter % 8 == 0 && tokens <= 65535 &&
+        ((uintptr_t)in | (uintptr_t)out) % 16 == 0) {
+        const int threads = inter >= 2048 ? 256 : 64;
+        dim3 grid((inter / 8 + threads - 1) / threads, tokens);
+        swiglu_bf16x8_kernel<<<grid, threads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter);
+        LLME_LAUNCH_STATUS();
+    }
     const long long total = (long long)tokens * inter;
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;

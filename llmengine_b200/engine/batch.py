@@ -44,6 +44,7 @@ class StepBatch:
     decode_rows: torch.Tensor       # int32 [ND] batch rows of the requests with exactly one token in this step
     portion_rows: torch.Tensor      # int32 [NP] batch rows of the other requests
     groups: List[GroupView] = field(default_factory=list)
+    assume_ctx: Optional[int] = None   # set when the step is (to be) captured: size launches for this context length
 
     @property
     def max_q_len(self) -> int:
@@ -59,6 +60,8 @@ class StepBatch:
 
     @property
     def max_decode_ctx(self) -> int:
+        if self.assume_ctx is not None:
+            return self.assume_ctx
         return max((s + 1 for s, q in zip(self.start_positions, self.q_lens) if q == 1), default=0)
 
     @property

@@ -88,6 +88,12 @@ class Engine:
                 self._caches.append(None)
         self._init_metadata()
         self.steps = 0
+        # decode-only steps are captured in CUDA graphs, one per batch size, after one eager step of that size
+        self.graphs_enabled = (bool(ec.use_cuda_graphs) and self.device.type == "cuda"
+                               and all(p.capture_safe for p in self.model.parts()))
+        self._graphs: Dict[int, tuple] = {}
+        self._graph_seen: set = set()
+        self._graph_pool = None
 
     # ------------------------------------------------------------------ sizing
     def _tokens_from_free_memory(self, specs) -> int:
@@ -243,12 +249,44 @@ class Engine:
         if entries:
             batch = self._build_batch(list(entries), starts)
             self.cache.flush()
-            logits = self.model.forward(batch, self._caches)
+            logits = self._forward(batch)
             for e, s in zip(entries, starts):
                 self.cache.advance(e.request, s + len(e.tokens))
             self.steps += 1
         for r in end:
             self.cache.free_request(r)
+        return logits
+
+    def _forward(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        """Eager launch sequence, or the replay of a captured one for decode-only steps in which every
+        request wants its logits.  What a captured step bakes in is only the number of requests; tokens,
+        positions, lengths and block tables are data in device buffers that are rewritten before each replay."""
+        R = batch.num_requests
+        if not (self.graphs_enabled and batch.decode_only and batch.logit_rows.numel() == R):
+            return self.model.forward(batch, self._caches)
+        rec = self._graphs.get(R)
+        if rec is not None:
+            graph, logits, launches, _keep = rec
+            graph.replay()
+            self.ops.launches += launches
+            return logits
+        batch.assume_ctx = self.max_model_len           # launch shapes must serve any later context length
+        if R not in self._graph_seen:                   # first step of this size: eager, so every buffer exists
+            self._graph_seen.add(R)
+            return self.model.forward(batch, self._caches)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = self.ops.launches
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(batch, self._caches)
+        launches = self.ops.launches - before
+        self.ops.launches = before
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        # the captured kernels hold raw pointers into the workspace: keep those buffers alive with the graph
+        self._graphs[R] = (graph, logits, launches, dict(self.rt._buffers))
+        graph.replay()
+        self.ops.launches += launches
         return logits
 
     def _undo(self, created, grown) -> None:

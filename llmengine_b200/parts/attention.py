@@ -126,9 +126,9 @@ class GQAttention(Part):
             ops.attention_decode(rows=batch.decode_rows, splits=splits, scratch=scratch, **meta, **common)
 
     def decode_splits(self, n_requests: int, max_ctx: int) -> int:
-        """Blocks per (request, key/value head): enough to give every SM about two blocks, never more
-        than there are 64-key tiles in the longest (windowed) context."""
+        """Blocks per (request, key/value head): as many as fit the GPU in one wave (148 SMs, two blocks
+        each), never more than there are 64-key groups in the longest (windowed) context."""
         span = min(max_ctx, self.window) if self.window > 0 else max_ctx
-        tiles = max(1, -(-span // 64) + (1 if self.window > 0 else 0))
+        groups = max(1, -(-span // 64) + (1 if self.window > 0 else 0))
         blocks = n_requests * self.nkv * (-(-(self.nh // self.nkv) // 16))
-        return max(1, min(tiles, -(-2 * 148 // blocks), 64))
+        return max(1, min(groups, (2 * 148) // blocks, 64))

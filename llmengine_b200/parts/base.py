@@ -65,6 +65,10 @@ class StateSpec:
 class Part:
     """Base class: holds the runtime and the tensor-name prefix."""
 
+    # False for a part whose forward reads device data on the host (it then cannot be captured in a
+    # CUDA graph, and steps of a model that holds such a part always run eagerly)
+    capture_safe = True
+
     def __init__(self, rt: "Runtime", prefix: str):
         self.rt = rt
         self.prefix = prefix

@@ -28,6 +28,7 @@ class PreNormResidualBlock(Part):
         self.ffn_norm = build_part("norm", layer.feed_forward_norm, rt, self.name(feed_forward_norm_name))
         self.ffn = build_part("feed_forward", layer.feed_forward, rt, self.name(feed_forward_name))
         self.parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        self.capture_safe = all(p.capture_safe for p in self.parts)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         out: Dict[str, WeightSpec] = {}

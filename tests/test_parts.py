@@ -172,6 +172,8 @@ class ToyDecayingSum(Part):
     one portion to the next through the request's state slot.  Written with plain tensor operations;
     it exists only to show that a mixer of another kind plugs in."""
 
+    capture_safe = False          # reads slot numbers on the host
+
     def __init__(self, rt, prefix, hidden_size, decay):
         super().__init__(rt, prefix)
         self.hidden, self.decay = hidden_size, decay
