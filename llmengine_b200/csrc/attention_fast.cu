@@ -201,6 +201,8 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
 
 // ----------------------------------------------------------------------------- portions
 __global__ void __launch_bounds__(THREADS) attention_portion_kernel(FastAttnArgs a) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS]
     bf16* Ks = Qs + BM * LDS;                              // [2][BN][LDS]
@@ -342,6 +344,8 @@ __device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, cons
 }
 
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs a) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][LDS]
     bf16* stages = Qs + 16 * LDS;                              // [4 warps][DSTAGES][K 16 rows | V 16 rows][LDS]
@@ -488,6 +492,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
 // split each (maximum and total weight), then one output column each; the loads of a loop do not depend
 // on each other, so they are in flight together.
 __global__ void attention_combine_kernel(FastAttnArgs a) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int idx = blockIdx.x * (blockDim.x >> 5) + warp;
     if (idx >= a.n_rows * a.nh) return;
@@ -558,7 +564,7 @@ LLME_API int llme_attention_portion(const FastAttnArgs* args, int max_q_len, cud
     const long long tiles = ((long long)max_q_len * G + BM - 1) / BM;
     if (tiles > 2147483647LL || a.nkv > 65535) LLME_REFUSE("attention: grid too large");
     dim3 grid((unsigned)tiles, a.nkv, a.n_rows);
-    attention_portion_kernel<<<grid, THREADS, PORTION_SMEM, stream>>>(a);
+    llme_launch(attention_portion_kernel, dim3(grid), dim3(THREADS), PORTION_SMEM, stream, a);
     LLME_LAUNCH_STATUS();
 }
 
@@ -578,10 +584,10 @@ LLME_API int llme_attention_decode(const FastAttnArgs* args, cudaStream_t stream
     const int chunks = (G + 15) / 16;
     if ((long long)a.nkv * chunks > 65535) LLME_REFUSE("attention: grid too large");
     dim3 grid(a.splits, a.nkv * chunks, a.n_rows);
-    attention_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(a);
+    llme_launch(attention_decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, stream, a);
     if (a.splits > 1) {
         const int warps = a.n_rows * a.nh;
-        attention_combine_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(a);
+        llme_launch(attention_combine_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, a);
     }
     LLME_LAUNCH_STATUS();
 }

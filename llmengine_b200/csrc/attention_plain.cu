@@ -28,6 +28,8 @@ struct AttnArgs {
 
 template <typename T, int REGS>
 __global__ void attention_plain_kernel(AttnArgs a) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -85,11 +87,11 @@ static int launch_plain(const AttnArgs& a, cudaStream_t s) {
     const int wpb = 4;
     dim3 grid((a.tokens + wpb - 1) / wpb, a.nh);
     const int regs = (a.hd + 31) / 32;
-    if (regs <= 1) attention_plain_kernel<T, 1><<<grid, wpb * 32, 0, s>>>(a);
-    else if (regs <= 2) attention_plain_kernel<T, 2><<<grid, wpb * 32, 0, s>>>(a);
-    else if (regs <= 4) attention_plain_kernel<T, 4><<<grid, wpb * 32, 0, s>>>(a);
-    else if (regs <= 8) attention_plain_kernel<T, 8><<<grid, wpb * 32, 0, s>>>(a);
-    else if (regs <= 16) attention_plain_kernel<T, 16><<<grid, wpb * 32, 0, s>>>(a);
+    if (regs <= 1) llme_launch(attention_plain_kernel<T, 1>, dim3(grid), dim3(wpb * 32), 0, s, a);
+    else if (regs <= 2) llme_launch(attention_plain_kernel<T, 2>, dim3(grid), dim3(wpb * 32), 0, s, a);
+    else if (regs <= 4) llme_launch(attention_plain_kernel<T, 4>, dim3(grid), dim3(wpb * 32), 0, s, a);
+    else if (regs <= 8) llme_launch(attention_plain_kernel<T, 8>, dim3(grid), dim3(wpb * 32), 0, s, a);
+    else if (regs <= 16) llme_launch(attention_plain_kernel<T, 16>, dim3(grid), dim3(wpb * 32), 0, s, a);
     else LLME_REFUSE("attention: head_dim %d is larger than 512", a.hd);
     LLME_LAUNCH_STATUS();
 }

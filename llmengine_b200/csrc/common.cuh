@@ -39,6 +39,43 @@ inline char* llme_error_buffer() {
         return (int)e__;                                              \
     } while (0)
 
+// Programmatic dependent launch.  A kernel launched through llme_launch may begin while the kernel
+// before it in the stream is still running (its blocks become resident once every block of the earlier
+// kernel has started); what it reads from or writes to memory that the earlier kernel touches must come
+// after pdl_wait(), which returns when the earlier kernel has completed.  Work that does not depend on
+// it (reading weights) may come first.  pdl_launch_dependents() lets the next kernel be scheduled early.
+// Both are no-ops for kernels launched the ordinary way.  It is off unless LLME_PDL=1 is set in the
+// environment: measured inside CUDA graphs on B200 (Qwen3-8B shape, batch 8) the decode step took 4.84 ms
+// with it and 4.57 ms without, so for now the launches are ordinary ones.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+#include <utility>
+inline bool llme_pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("LLME_PDL");
+        return e && e[0] == '1';
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t llme_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = llme_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

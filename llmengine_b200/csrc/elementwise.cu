@@ -16,6 +16,8 @@ LLME_API const char* llme_last_error() { return llme_error_buffer(); }
 template <typename W>
 __global__ void embedding_kernel(const int* __restrict__ ids, const W* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -30,6 +32,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const W* __restric
 // The same for bfloat16 tables whose rows are a multiple of 8 wide: 16 bytes in, 32 bytes out per thread.
 __global__ void embedding_bf16x8_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -56,13 +60,13 @@ LLME_API int llme_embedding(const int* ids, const void* table, int table_dtype, 
     if (!ids || !table || !out || hidden <= 0 || vocab <= 0) LLME_REFUSE("embedding: null pointer or non-positive size");
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == LLME_BF16 && hidden % 8 == 0 && ((uintptr_t)table % 16) == 0 && ((uintptr_t)out % 16) == 0) {
-        embedding_bf16x8_kernel<<<tokens, hidden >= 2048 ? 256 : 64, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+        llme_launch(embedding_bf16x8_kernel, dim3(tokens), dim3(hidden >= 2048 ? 256 : 64), 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab);
         LLME_LAUNCH_STATUS();
     }
     if (table_dtype == LLME_F32)
-        embedding_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+        llme_launch(embedding_kernel<float>, dim3(tokens), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab);
     else if (table_dtype == LLME_BF16)
-        embedding_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+        llme_launch(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab);
     else
         LLME_REFUSE("embedding: unsupported table dtype %d", table_dtype);
     LLME_LAUNCH_STATUS();
@@ -75,6 +79,8 @@ LLME_API int llme_embedding(const int* ids, const void* table, int table_dtype, 
 template <typename D, typename G, typename O, bool HAS_DELTA>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const D* __restrict__ delta, const G* __restrict__ gain,
                                O* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -123,6 +129,8 @@ template <> struct Vec4<__nv_bfloat16> {
 template <typename D, typename G, typename O, bool HAS_DELTA, int V>
 __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const D* __restrict__ delta, const G* __restrict__ gain,
                                    O* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -170,11 +178,11 @@ static bool launch_rmsnorm_vec(float* x, const void* delta, const void* gain, vo
     const int groups = hidden / 4;
     // few rows: short dependency chains matter more than occupancy, so spread the row over many threads
     if (groups <= 256)
-        rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 1><<<n_out, ((groups + 31) / 32) * 32, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 1>, dim3(n_out), dim3(((groups + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
     else if (groups <= 1024)
-        rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 2><<<n_out, (((groups + 1) / 2 + 31) / 32) * 32, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 2>, dim3(n_out), dim3((((groups + 1) / 2 + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
     else
-        rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 4><<<n_out, (((groups + 3) / 4 + 31) / 32) * 32, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+        llme_launch(rmsnorm_vec_kernel<D, G, O, HAS_DELTA, 4>, dim3(n_out), dim3((((groups + 3) / 4 + 31) / 32) * 32), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
     return true;
 }
 
@@ -183,7 +191,7 @@ static void launch_rmsnorm(float* x, const void* delta, const void* gain, void* 
                            int n_out, int hidden, float eps, cudaStream_t s) {
     if (launch_rmsnorm_vec<D, G, O, HAS_DELTA>(x, delta, gain, out, rows, n_out, hidden, eps, s)) return;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    rmsnorm_kernel<D, G, O, HAS_DELTA><<<n_out, threads, 0, s>>>(x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
+    llme_launch(rmsnorm_kernel<D, G, O, HAS_DELTA>, dim3(n_out), dim3(threads), 0, s, x, (const D*)delta, (const G*)gain, (O*)out, rows, hidden, eps);
 }
 
 template <typename D, bool HAS_DELTA>
@@ -234,6 +242,8 @@ struct QkvArgs {
 
 template <typename I, typename O, typename G>
 __global__ void qkv_post_kernel(QkvArgs a) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -328,6 +338,8 @@ template <> struct Vec2<__nv_bfloat16> {
 
 template <typename I, typename O, typename G, int NP>
 __global__ void qkv_post_vec_kernel(QkvArgs a) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -435,9 +447,9 @@ static bool launch_qkv_vec(const QkvArgs& a, unsigned blocks, int threads, cudaS
                            (uintptr_t)a.cache;
     if (ptrs % 8) return false;
     const int half = a.hd / 2;
-    if (half <= 64) qkv_post_vec_kernel<I, O, G, 1><<<blocks, threads, 0, s>>>(a);
-    else if (half <= 128) qkv_post_vec_kernel<I, O, G, 2><<<blocks, threads, 0, s>>>(a);
-    else qkv_post_vec_kernel<I, O, G, 4><<<blocks, threads, 0, s>>>(a);
+    if (half <= 64) llme_launch(qkv_post_vec_kernel<I, O, G, 1>, dim3(blocks), dim3(threads), 0, s, a);
+    else if (half <= 128) llme_launch(qkv_post_vec_kernel<I, O, G, 2>, dim3(blocks), dim3(threads), 0, s, a);
+    else llme_launch(qkv_post_vec_kernel<I, O, G, 4>, dim3(blocks), dim3(threads), 0, s, a);
     return true;
 }
 
@@ -452,8 +464,8 @@ static int dispatch_qkv_gain(const QkvArgs& a, cudaStream_t s) {
     } else if (a.gain_dtype == LLME_BF16) {
         if (launch_qkv_vec<I, O, __nv_bfloat16>(a, (unsigned)blocks, wpb * 32, s)) LLME_LAUNCH_STATUS();
     }
-    if (a.gain_dtype == LLME_F32) qkv_post_kernel<I, O, float><<<(unsigned)blocks, wpb * 32, 0, s>>>(a);
-    else if (a.gain_dtype == LLME_BF16) qkv_post_kernel<I, O, __nv_bfloat16><<<(unsigned)blocks, wpb * 32, 0, s>>>(a);
+    if (a.gain_dtype == LLME_F32) llme_launch(qkv_post_kernel<I, O, float>, dim3((unsigned)blocks), dim3(wpb * 32), 0, s, a);
+    else if (a.gain_dtype == LLME_BF16) llme_launch(qkv_post_kernel<I, O, __nv_bfloat16>, dim3((unsigned)blocks), dim3(wpb * 32), 0, s, a);
     else LLME_REFUSE("qkv_post: unsupported gain dtype %d", a.gain_dtype);
     LLME_LAUNCH_STATUS();
 }
@@ -476,6 +488,8 @@ LLME_API int llme_qkv_post(const QkvArgs* args, int in_dtype, int out_dtype, cud
 // in [T, 2*inter] = gate | up;  out[t, i] = gate / (1 + exp(-gate)) * up.
 template <typename I, typename O>
 __global__ void swiglu_kernel(const I* __restrict__ in, O* __restrict__ out, long long total, int inter) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -489,6 +503,8 @@ __global__ void swiglu_kernel(const I* __restrict__ in, O* __restrict__ out, lon
 
 // Vector form: 8 values per thread (two 16-byte loads, one 16-byte store for bfloat16), grid (column chunks, tokens).
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int inter) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= inter) return;
     const size_t t = blockIdx.y;
@@ -514,18 +530,18 @@ LLME_API int llme_swiglu(const void* in, int in_dtype, void* out, int out_dtype,
         ((uintptr_t)in | (uintptr_t)out) % 16 == 0) {
         const int threads = inter >= 2048 ? 256 : 64;
         dim3 grid((inter / 8 + threads - 1) / threads, tokens);
-        swiglu_bf16x8_kernel<<<grid, threads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter);
+        llme_launch(swiglu_bf16x8_kernel, dim3(grid), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter);
         LLME_LAUNCH_STATUS();
     }
     const long long total = (long long)tokens * inter;
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (in_dtype == LLME_F32 && out_dtype == LLME_F32)
-        swiglu_kernel<float, float><<<(unsigned)blocks, 256, 0, stream>>>((const float*)in, (float*)out, total, inter);
+        llme_launch(swiglu_kernel<float, float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)in, (float*)out, total, inter);
     else if (in_dtype == LLME_BF16 && out_dtype == LLME_BF16)
-        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, inter);
+        llme_launch(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, inter);
     else if (in_dtype == LLME_F32 && out_dtype == LLME_BF16)
-        swiglu_kernel<float, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, total, inter);
+        llme_launch(swiglu_kernel<float, __nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)in, (__nv_bfloat16*)out, total, inter);
     else
         LLME_REFUSE("swiglu: unsupported in/out dtype %d/%d", in_dtype, out_dtype);
     LLME_LAUNCH_STATUS();

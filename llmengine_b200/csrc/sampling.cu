@@ -16,6 +16,8 @@ LLME_API const char* llme_last_error() { return llme_error_buffer(); }
 // (src/runtime/sampler.cpp:22-32).  The (row, token) pairs must be distinct.
 __global__ void repetition_penalty_kernel(float* logits, long long ld, const int* row, const int* token,
                                           const int* count, const float* penalty, int pairs, int vocab) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= pairs) return;
     const int tok = token[i];
@@ -32,7 +34,7 @@ LLME_API int llme_repetition_penalty(float* logits, long long ld, const int* row
                                      const float* penalty, int pairs, int vocab, cudaStream_t stream) {
     if (pairs <= 0) return 0;
     if (!logits || !row || !token || !count || !penalty) LLME_REFUSE("repetition_penalty: null pointer");
-    repetition_penalty_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(logits, ld, row, token, count, penalty, pairs, vocab);
+    llme_launch(repetition_penalty_kernel, dim3((pairs + 255) / 256), dim3(256), 0, stream, logits, ld, row, token, count, penalty, pairs, vocab);
     LLME_LAUNCH_STATUS();
 }
 
@@ -63,6 +65,8 @@ __device__ __forceinline__ int block_sum_int(int v, int* scratch) {
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
     __shared__ float fs[32];
     __shared__ int is[32];
     __shared__ float prefix[SAMPLE_THREADS + 1];
@@ -201,6 +205,6 @@ LLME_API int llme_sample(const SampleArgs* args, cudaStream_t stream) {
     if (a.rows <= 0) return 0;
     if (!a.logits || !a.out || a.vocab <= 0 || a.ld < a.vocab) LLME_REFUSE("sample: null pointer or bad sizes");
     if (!a.u) LLME_REFUSE("sample: the uniform numbers are missing");
-    sample_kernel<<<a.rows, SAMPLE_THREADS, 0, stream>>>(a);
+    llme_launch(sample_kernel, dim3(a.rows), dim3(SAMPLE_THREADS), 0, stream, a);
     LLME_LAUNCH_STATUS();
 }

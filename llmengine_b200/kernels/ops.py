@@ -269,6 +269,15 @@ class CudaOps:
         assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
         if M == 0:
             return out
+        if (M <= 16 and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            # a handful of tokens: this package's weight-streaming kernel
+            lib = self._lib("gemm_skinny")
+            rc = lib.llme_gemm_skinny_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w.data_ptr()),
+                                           c_longlong(w.stride(0)), c_void_p(out.data_ptr()), c_int(_code(out.dtype)),
+                                           c_longlong(out.stride(0)), c_int(M), c_int(N), c_int(K), self._stream())
+            self._check(lib, rc, "gemm_skinny")
+            return out
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
         else:

@@ -125,6 +125,36 @@ def test_linear_bf16(ops, M, N, K):
     assert (out16.cpu().float() - want).abs().max() < 0.02 * want.abs().max()
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 100, 72), (16, 1000, 264), (9, 33, 8),
+                                   (5, 24576, 512), (2, 151936, 128), (8, 4096, 12288)])
+def test_skinny_gemm(ops, M, N, K, out_dtype):
+    """The decode-step product (at most 16 tokens): rows and widths that are no multiple of the tiles."""
+    a = _rand(M, K, dtype=torch.bfloat16, seed=40)
+    w = _rand(N, K, dtype=torch.bfloat16, seed=41, scale=0.05)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear(a, w, out)
+    want = (a.double() @ w.double().t()).cpu()
+    got = out.double().cpu()
+    assert torch.isfinite(got).all()
+    tol = 2e-5 * math.sqrt(K) * float(want.abs().max() + 1)
+    if out_dtype == torch.bfloat16:
+        assert ((got - want).abs() <= want.abs() * 2 ** -8 + tol).all()
+    else:
+        assert (got - want).abs().max() < tol
+
+
+def test_skinny_gemm_rows_do_not_depend_on_the_batch(ops):
+    a = _rand(16, 1024, dtype=torch.bfloat16, seed=42)
+    w = _rand(300, 1024, dtype=torch.bfloat16, seed=43)
+    full = torch.empty(16, 300, device=DEV)
+    ops.linear(a, w, full)
+    for m in (1, 7, 8, 9):
+        part = torch.empty(m, 300, device=DEV)
+        ops.linear(a[:m].contiguous(), w, part)
+        assert torch.equal(part, full[:m])
+
+
 # ----------------------------------------------------------------------------- QK norm + rope + cache write
 def _paged_layout(T, page_size, num_pages, seed):
     """Scatter T consecutive positions over pages in a scrambled order."""
