@@ -29,6 +29,7 @@ SOURCES: Dict[str, str] = {
     "gemm_f32": "gemm_f32.cu",
     "sampling": "sampling.cu",
     "gemm_skinny": "gemm_skinny.cu",
+    "gemm_tcgen05": "gemm_tcgen05.cu",
     # compiled per head size: ask for "attention_fast@HEAD_DIM=128"
     "attention_fast": "attention_fast.cu",
     # the same kernels with built-in scratch memory: "attention_decode_static@HEAD_DIM=128"

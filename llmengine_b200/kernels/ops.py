@@ -284,6 +284,22 @@ class CudaOps:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         return out
 
+    def linear_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out[M,N] = x[M,K] @ w[N,K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory)."""
+        lib = self._lib("gemm_tcgen05")
+        M, K = x.shape
+        N = w.shape[0]
+        assert x.dtype == w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+        rc = lib.llme_gemm_tc_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w.data_ptr()),
+                                   c_longlong(w.stride(0)), c_void_p(out.data_ptr()), c_int(_code(out.dtype)),
+                                   c_longlong(out.stride(0)), c_int(M), c_int(N), c_int(K), self._stream())
+        self._check(lib, rc, "gemm_tcgen05")
+        return out
+
+    def linear_tc_status(self) -> int:
+        """0 if no bounded wait of the tcgen05 kernels ever gave up (synchronises the device)."""
+        return int(self._lib("gemm_tcgen05").llme_gemm_tc_status())
+
     def repetition_penalty(self, logits, rows, tokens, counts, penalty) -> None:
         lib = self._lib("sampling")
         rc = lib.llme_repetition_penalty(c_void_p(logits.data_ptr()), c_longlong(logits.stride(0)),
