@@ -111,38 +111,59 @@ __device__ __forceinline__ void tmem_ld_32x32(unsigned addr, unsigned (&v)[32]) 
 struct TcArgs {
     void* out; long long ldo;
     int M, N, K;
+    int m_tiles, n_tiles;
 };
 
-template <int BN, int STAGES, typename O>
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+
+// Persistent kernel: one block per SM walks over the output tiles (m fastest, so blocks that run together
+// share a tile of W).  The accumulator is double-buffered in tensor memory (2 x BN columns): while the
+// epilogue warps read tile i out of one buffer, the MMA warp already fills the other with tile i+1.
+// TMA_STORE: the epilogue stages 32-row x 128-byte pieces in (swizzled) shared memory and writes them with
+// cp.async.bulk.tensor stores; otherwise it stores from registers (any alignment of the output).
+template <int BN, int STAGES, typename O, bool TMA_STORE>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_o, TcArgs a) {
     extern __shared__ unsigned char smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr int STAGING = TMA_STORE ? 4 * 2 * 4096 : 0;          // 4 warps x 2 buffers x (32 rows x 128 bytes)
     unsigned char* a_tiles = smem;
     unsigned char* b_tiles = smem + STAGES * A_BYTES;
-    unsigned long long* full = reinterpret_cast<unsigned long long*>(b_tiles + STAGES * B_BYTES);
+    unsigned char* staging = b_tiles + STAGES * B_BYTES;
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(staging + STAGING);
     unsigned long long* empty = full + STAGES;
-    unsigned long long* acc_full = empty + STAGES;
-    unsigned* tmem_holder = reinterpret_cast<unsigned*>(acc_full + 1);
+    unsigned long long* acc_full = empty + STAGES;                 // [2]
+    unsigned long long* acc_empty = acc_full + 2;                  // [2]
+    unsigned* tmem_holder = reinterpret_cast<unsigned*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int k_blocks = (a.K + BK - 1) / BK;
-    constexpr unsigned TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+    const int tiles = a.m_tiles * a.n_tiles;
+    constexpr unsigned TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
         }
-        mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full + b, 1);
+            mbar_init(acc_empty + b, 4);          // one arrival per epilogue warp
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {                      // one warp allocates the accumulator's tensor memory
+    if (warp == 1) {                      // one warp allocates the accumulators' tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
@@ -154,86 +175,133 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(empty + s, ((kb / STAGES) - 1) & 1, abort_flag, 1)) break;
-                if (*abort_flag) break;
-                mbar_expect_tx(full + s, A_BYTES + B_BYTES);
-                tma_load_2d(a_tiles + s * A_BYTES, &map_x, kb * BK, m0, full + s);
-                tma_load_2d(b_tiles + s * B_BYTES, &map_w, kb * BK, n0, full + s);
-                issued = kb + 1;
-            }
-            if (*abort_flag) {
-                // gave up somewhere: let the copies that are still in flight land before the block exits
-                for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
-                    const int s = kb % STAGES;
-                    for (unsigned i = 0; i < WAIT_LIMIT && !mbar_try_wait(full + s, (kb / STAGES) & 1); ++i) {}
+            unsigned it = 0, first_in_flight = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const int m0 = (t % a.m_tiles) * BM, n0 = (t / a.m_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const unsigned s = it % STAGES;
+                    ok = mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, 1) && !*abort_flag;
+                    if (!ok) break;
+                    mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+                    tma_load_2d(a_tiles + s * A_BYTES, &map_x, kb * BK, m0, full + s);
+                    tma_load_2d(b_tiles + s * B_BYTES, &map_w, kb * BK, n0, full + s);
                 }
+            }
+            if (!ok) {
+                // gave up somewhere: let the copies that may still be in flight land before the block exits
+                first_in_flight = it > STAGES ? it - STAGES : 0;
+                for (unsigned j = first_in_flight; j < it; ++j)
+                    for (unsigned i = 0; i < WAIT_LIMIT && !mbar_try_wait(full + j % STAGES, (j / STAGES) & 1); ++i) {}
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr unsigned idesc = umma_idesc(BM, BN);
+            unsigned it = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(full + s, (kb / STAGES) & 1, abort_flag, 2);
+            int i = 0;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++i) {
+                const int b = i & 1;
+                ok = mbar_wait(acc_empty + b, ((i >> 1) & 1) ^ 1, abort_flag, 4);   // the epilogue has drained this buffer
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned long long da = umma_desc(a_tiles + s * A_BYTES);
-                const unsigned long long db = umma_desc(b_tiles + s * B_BYTES);
+                const unsigned tmem_d = tmem_base + (unsigned)(b * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const unsigned s = it % STAGES;
+                    ok = mbar_wait(full + s, (it / STAGES) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned long long da = umma_desc(a_tiles + s * A_BYTES);
+                    const unsigned long long db = umma_desc(b_tiles + s * B_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // the next 16 k values lie 32 bytes further inside the swizzled rows: +2 in the address field
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // the next 16 k values lie 32 bytes further inside the swizzled rows: +2 in the address field
+                        umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty + s);       // the stage is free once these instructions have read it
                 }
-                umma_commit(empty + s);           // the stage is free once these instructions have read it
+                umma_commit(acc_full + b);        // all of the tile's instructions done: the accumulator is complete
             }
-            umma_commit(acc_full);                // all instructions done: the accumulator is complete
         }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int quarter = warp & 3;             // the TMEM lanes this warp may read: 32 * (warp % 4) ...
-        const bool ok = mbar_wait(acc_full, 0, abort_flag, 3);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        constexpr int COLS = 128 / (int)sizeof(O);    // output columns per 128-byte staging row
+        unsigned char* my_staging = staging + quarter * 2 * 4096;
+        int i = 0, piece = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++i) {
+            const int m0 = (t % a.m_tiles) * BM, n0 = (t / a.m_tiles) * BN;
+            const int b = i & 1;
+            ok = mbar_wait(acc_full + b, (i >> 1) & 1, abort_flag, 3);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + quarter * 32 + lane;
+            const unsigned tmem_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(b * BN);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                unsigned v[32];
-                tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(c * 32), v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int col = n0 + c * 32;
-                if (row < a.M && col < a.N) {
-                    O* dst = reinterpret_cast<O*>(a.out) + (size_t)row * a.ldo + col;
-                    if (col + 32 <= a.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            for (int c = 0; c < BN; c += COLS) {
+                unsigned char* buf = my_staging + (piece & 1) * 4096;
+                if (TMA_STORE) {
+                    // the store that last used this buffer (two pieces ago) must have read it
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int half = 0; half < COLS / 32; ++half) {
+                    unsigned v[32];
+                    tmem_ld_32x32(tmem_row + (unsigned)(c + half * 32), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (c + COLS >= BN && half == COLS / 32 - 1) {
+                        // the tile has left tensor memory: hand the buffer back to the MMA warp
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty + b);
+                    }
+                    if (TMA_STORE) {
+                        // row `lane` of the piece; its 16-byte chunk q goes to position q ^ (lane % 8): the 128-byte swizzle
                         if (sizeof(O) == 4) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            for (int q = 0; q < 8; ++q)
+                                *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+                                    make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
+                            for (int q = 0; q < 4; ++q) {
                                 uint4 pk;
                                 unsigned* pw = reinterpret_cast<unsigned*>(&pk);
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]), __uint_as_float(v[8 * q + 2 * e + 1]));
                                     pw[e] = *reinterpret_cast<unsigned*>(&h);
                                 }
-                                reinterpret_cast<uint4*>(dst)[j] = pk;
+                                *reinterpret_cast<uint4*>(buf + lane * 128 + (((half * 4 + q) ^ (lane & 7)) << 4)) = pk;
                             }
                         }
                     } else {
+                        const int col = n0 + c + half * 32;
+                        if (row < a.M && col < a.N) {
+                            O* dst = reinterpret_cast<O*>(a.out) + (size_t)row * a.ldo + col;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < a.N) dst[j] = from_f32<O>(__uint_as_float(v[j]));
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < a.N) dst[j] = from_f32<O>(__uint_as_float(v[j]));
+                        }
                     }
+                }
+                if (TMA_STORE) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the generic-proxy writes above, seen by the TMA
+                    __syncwarp();
+                    if (lane == 0) {
+                        // rows or columns of the piece that lie outside the matrix are clipped by the TMA
+                        if (m0 + quarter * 32 < a.M && n0 + c < a.N) tma_store_2d(&map_o, buf, n0 + c, m0 + quarter * 32);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    ++piece;
                 }
             }
         }
+        if (TMA_STORE && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -257,38 +325,64 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// A [rows, K] bfloat16 matrix with row stride ld (elements), cut into boxes of box_rows x 64, 128-byte swizzle;
-// parts of a box outside the matrix read as zeros.
-int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+// A [rows, cols] matrix with row stride ld (elements of `elem_bytes`), cut into boxes of box_rows x box_cols,
+// 128-byte swizzle (box_cols * elem_bytes = 128); parts of a box outside the matrix read as zeros and are
+// not written.
+int make_map(CUtensorMap* map, const void* base, CUtensorMapDataType type, int elem_bytes, long long rows, long long cols,
+             long long ld, int box_rows, int box_cols) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) LLME_REFUSE("gemm_tc: cuTensorMapEncodeTiled is not available in this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = enc(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) LLME_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
     return 0;
 }
 
-template <int BN, int STAGES, typename O>
-int launch(const void* x, long long ldx, const void* w, long long ldw, const TcArgs& a, cudaStream_t s) {
-    alignas(64) CUtensorMap mx, mw;
-    if (int rc = make_map(&mx, x, a.M, a.K, ldx, BM)) return rc;
-    if (int rc = make_map(&mw, w, a.N, a.K, ldw, BN)) return rc;
-    constexpr size_t smem = 1024 + (size_t)STAGES * (BM + BN) * BK * 2 + (2 * STAGES + 1) * 8 + 16;
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) v = 148;
+        return v;
+    }();
+    return n;
+}
+
+template <int BN, int STAGES, typename O, bool TMA_STORE>
+int launch_kernel(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const TcArgs& a, cudaStream_t s) {
+    constexpr size_t smem = 1024 + (size_t)STAGES * (BM + BN) * BK * 2 + (TMA_STORE ? 4 * 2 * 4096 : 0) + (2 * STAGES + 4) * 8 + 16;
+    static_assert(smem <= 232448, "the block's shared memory must fit an SM");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, O>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, O, TMA_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LLME_REFUSE("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
-    if (grid.y > 65535) LLME_REFUSE("gemm_tc: M = %d needs more than 65535 row tiles", a.M);
-    gemm_tc_kernel<BN, STAGES, O><<<grid, THREADS, smem, s>>>(mx, mw, a);
+    const int tiles = a.m_tiles * a.n_tiles;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    gemm_tc_kernel<BN, STAGES, O, TMA_STORE><<<grid, THREADS, smem, s>>>(mx, mw, mo, a);
     LLME_LAUNCH_STATUS();
+}
+
+template <int BN, int STAGES, typename O>
+int launch(const void* x, long long ldx, const void* w, long long ldw, TcArgs a, cudaStream_t s) {
+    alignas(64) CUtensorMap mx, mw, mo;
+    if (int rc = make_map(&mx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.M, a.K, ldx, BM, BK)) return rc;
+    if (int rc = make_map(&mw, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.N, a.K, ldw, BN, BK)) return rc;
+    a.m_tiles = (a.M + BM - 1) / BM;
+    a.n_tiles = (a.N + BN - 1) / BN;
+    // a TMA store needs a 16-byte aligned base and row stride
+    const bool tma_store = ((uintptr_t)a.out % 16 == 0) && ((a.ldo * (long long)sizeof(O)) % 16 == 0);
+    if (tma_store) {
+        const CUtensorMapDataType t = sizeof(O) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        if (int rc = make_map(&mo, a.out, t, (int)sizeof(O), a.M, a.N, a.ldo, 32, 128 / (int)sizeof(O))) return rc;
+        return launch_kernel<BN, STAGES, O, true>(mx, mw, mo, a, s);
+    }
+    mo = mx;
+    return launch_kernel<BN, STAGES, O, false>(mx, mw, mo, a, s);
 }
 
 }  // namespace
@@ -306,7 +400,7 @@ LLME_API int llme_gemm_tc_bf16(const void* x, long long ldx, const void* w, long
     if (!x || !w || !out) LLME_REFUSE("gemm_tc: null pointer");
     if (!llme_gemm_tc_supports(M, N, K, ldx, ldw, ldo)) LLME_REFUSE("gemm_tc: M=%d N=%d K=%d ldx=%lld ldw=%lld ldo=%lld is not supported (K and operand strides must be multiples of 8)", M, N, K, ldx, ldw, ldo);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_tc: operands must be 16-byte aligned");
-    TcArgs a{out, ldo, M, N, K};
+    TcArgs a{out, ldo, M, N, K, 0, 0};
     if (out_dtype == LLME_F32) return N > 128 ? launch<256, 4, float>(x, ldx, w, ldw, a, stream) : launch<128, 6, float>(x, ldx, w, ldw, a, stream);
     if (out_dtype == LLME_BF16) return N > 128 ? launch<256, 4, bf16>(x, ldx, w, ldw, a, stream) : launch<128, 6, bf16>(x, ldx, w, ldw, a, stream);
     LLME_REFUSE("gemm_tc: unsupported output dtype %d", out_dtype);

@@ -63,6 +63,8 @@ class Engine:
         self.ops = ops
         self.spec = self.config.model_spec()
         self.max_model_len = min(ec.max_model_len or self.spec.max_positions, self.spec.max_positions)
+        if hasattr(ops, "use_tcgen05"):
+            ops.use_tcgen05 = ec.kernels == "fast"
         self.rt = Runtime(ops, self.device, self.dtype, ec.max_num_batched_tokens, ec.kernels)
         self.model = Model(self.spec, self.rt)
         if model_dir is not None:
@@ -306,3 +308,9 @@ class Engine:
 
     def free(self, request: Hashable) -> None:
         self.cache.free_request(request)
+
+    def check_kernels(self) -> None:
+        """Raise if a bounded wait inside a kernel ever gave up (synchronises the device)."""
+        status = self.ops.linear_tc_status() if hasattr(self.ops, "linear_tc_status") and "gemm_tcgen05" in getattr(self.ops, "_libs", {}) else 0
+        if status:
+            raise RuntimeError(f"a tcgen05 kernel gave up waiting (code {status}): its results are not valid")

@@ -90,6 +90,7 @@ class CudaOps:
         if self.device.type != "cuda":
             raise KernelsUnavailable(f"device {device} is not a CUDA device")
         self._libs: Dict[str, ctypes.CDLL] = {}
+        self.use_tcgen05 = True    # products of 128 tokens or more on this package's tcgen05 kernel, else cuBLAS
         self.launches = 0          # kernels of this package launched so far (cuBLAS calls are not counted)
 
     # ------------------------------------------------------------------ loading
@@ -278,6 +279,10 @@ class CudaOps:
                                            c_longlong(out.stride(0)), c_int(M), c_int(N), c_int(K), self._stream())
             self._check(lib, rc, "gemm_skinny")
             return out
+        if (self.use_tcgen05 and M >= 128 and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            # many tokens: this package's tcgen05 kernel (TMA-fed, accumulator in tensor memory)
+            return self.linear_tc(x, w, out)
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
         else:

@@ -126,6 +126,39 @@ def test_linear_bf16(ops, M, N, K):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 72), (129, 257, 264), (300, 1000, 96), (2048, 520, 1024),
+                                   (1000, 4096, 4096), (257, 24, 8)])
+def test_tcgen05_gemm(ops, M, N, K, out_dtype):
+    """The prompt-portion product on the tcgen05 tensor cores: tiles that hang over every edge, one and
+    many k blocks, more tiles than SMs."""
+    a = _rand(M, K, dtype=torch.bfloat16, seed=50)
+    w = _rand(N, K, dtype=torch.bfloat16, seed=51, scale=0.05)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear_tc(a, w, out)
+    assert ops.linear_tc_status() == 0, "a bounded wait gave up"
+    want = (a.double() @ w.double().t()).cpu()
+    got = out.double().cpu()
+    assert torch.isfinite(got).all()
+    tol = 2e-5 * math.sqrt(K) * float(want.abs().max() + 1)
+    if out_dtype == torch.bfloat16:
+        assert ((got - want).abs() <= want.abs() * 2 ** -8 + tol).all()
+    else:
+        assert (got - want).abs().max() < tol
+
+
+def test_tcgen05_gemm_into_a_strided_unaligned_output(ops):
+    """An output whose rows do not start on 16-byte boundaries takes the register-store epilogue."""
+    a = _rand(200, 128, dtype=torch.bfloat16, seed=52)
+    w = _rand(77, 128, dtype=torch.bfloat16, seed=53)
+    buf = torch.zeros(200, 81, device=DEV)
+    ops.linear_tc(a, w, buf[:, 1:78])
+    assert ops.linear_tc_status() == 0
+    want = (a.double() @ w.double().t()).cpu()
+    assert (buf[:, 1:78].double().cpu() - want).abs().max() < 1e-3
+    assert buf[:, 0].abs().max() == 0 and buf[:, 78:].abs().max() == 0
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 100, 72), (16, 1000, 264), (9, 33, 8),
                                    (5, 24576, 512), (2, 151936, 128), (8, 4096, 12288)])
 def test_skinny_gemm(ops, M, N, K, out_dtype):
