@@ -200,13 +200,41 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
 }
 
 // ----------------------------------------------------------------------------- portions
-__global__ void __launch_bounds__(THREADS) attention_portion_kernel(FastAttnArgs a) {
+// One warp: scores of its 16 query rows (fragments read from the shared Q tile at `Qw`) against NT*8 keys
+// starting at shared row `key0` of the K tile.  Reading the query fragments from shared memory at every
+// step instead of holding them costs a few loads and saves 4*KSTEPS registers per thread.
+template <int NT>
+__device__ __forceinline__ void qk_tile_shared_q(float (&s)[NT][4], const bf16* Qw, const bf16* Ks, int key0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+        unsigned qf[4];
+        ldmatrix_x4(qf, Qw + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+            unsigned b[4];
+            const int mi = lane >> 3;
+            ldmatrix_x4(b, Ks + (key0 + np * 16 + (lane & 7) + (mi >> 1) * 8) * LDS + kk * 16 + (mi & 1) * 8);
+            mma_bf16(s[2 * np], qf, b[0], b[1]);
+            mma_bf16(s[2 * np + 1], qf, b[2], b[3]);
+        }
+    }
+}
+
+// A block holds one copy of the K and V tiles (no double buffering) and at most 128 registers per
+// thread, so that four blocks (16 warps) share an SM and hide each other's waits; the scores of a 64-key
+// tile are formed 32 keys at a time.
+constexpr int PORTION_BLOCKS_PER_SM = HD <= 64 ? 6 : 4;
+
+__global__ void __launch_bounds__(THREADS, PORTION_BLOCKS_PER_SM) attention_portion_kernel(FastAttnArgs a) {
     pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     pdl_wait();                // everything below reads or writes what earlier kernels touch
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS]
-    bf16* Ks = Qs + BM * LDS;                              // [2][BN][LDS]
-    bf16* Vs = Ks + 2 * BN * LDS;                          // [2][BN][LDS]
+    bf16* Ks = Qs + BM * LDS;                              // [BN][LDS]
+    bf16* Vs = Ks + BN * LDS;                              // [BN][LDS]
 
     const int r = a.rows[blockIdx.z];
     const int kvh = blockIdx.y;
@@ -214,8 +242,9 @@ __global__ void __launch_bounds__(THREADS) attention_portion_kernel(FastAttnArgs
     const int q0 = a.cu_q_lens[r];
     const int q_len = a.cu_q_lens[r + 1] - q0;
     const int M = q_len * G;
-    const int m0 = blockIdx.x * BM;
-    if (m0 >= M) return;
+    // the tiles with the most keys (the last rows of the portion) start first
+    const int m0 = ((M + BM - 1) / BM - 1 - (int)blockIdx.x) * BM;
+    if (m0 < 0) return;
     const int start = a.ctx_lens[r] - q_len;               // position of the portion's first token
     const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -238,10 +267,6 @@ __global__ void __launch_bounds__(THREADS) attention_portion_kernel(FastAttnArgs
             cp_async_16(Qs + row * LDS + ch * 8, src, valid);
         }
     }
-    const int j_first = (lo_min / BN) * BN;
-    load_kv_tile(Ks, a.cache, bt, 0, kvh, a.nkv, a.page_size, j_first, lo_min, hi_max);
-    load_kv_tile(Vs, a.cache, bt, 1, kvh, a.nkv, a.page_size, j_first, lo_min, hi_max);
-    cp_async_commit();
 
     // this thread's two rows
     int plo[2], phi[2];
@@ -256,42 +281,41 @@ __global__ void __launch_bounds__(THREADS) attention_portion_kernel(FastAttnArgs
     float o[DTILES][4];
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
-    unsigned qf[KSTEPS][4];
     const float sc = a.scale * LOG2E;
+    const bf16* Qw = Qs + warp * 16 * LDS;
+    const int warp_hi = start + min(q_len - 1, (m0 + warp * 16 + 15) / G);
+    const int warp_lo = a.window > 0 ? max(0, start + (m0 + warp * 16) / G - a.window + 1) : 0;
+    const bool warp_has_rows = m0 + warp * 16 < M;
 
-    int buf = 0;
-    for (int j0 = j_first; j0 <= hi_max; j0 += BN) {
-        const int jn = j0 + BN;
-        if (jn <= hi_max) {
-            load_kv_tile(Ks + (buf ^ 1) * BN * LDS, a.cache, bt, 0, kvh, a.nkv, a.page_size, jn, lo_min, hi_max);
-            load_kv_tile(Vs + (buf ^ 1) * BN * LDS, a.cache, bt, 1, kvh, a.nkv, a.page_size, jn, lo_min, hi_max);
-        }
+    for (int j0 = (lo_min / BN) * BN; j0 <= hi_max; j0 += BN) {
+        load_kv_tile(Ks, a.cache, bt, 0, kvh, a.nkv, a.page_size, j0, lo_min, hi_max);
+        cp_async_commit();                                  // (the first group also carries the Q tile)
+        load_kv_tile(Vs, a.cache, bt, 1, kvh, a.nkv, a.page_size, j0, lo_min, hi_max);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<1>();                                 // the keys have landed, the values may still be on their way
         __syncthreads();
-        if (j0 == j_first) {
 #pragma unroll
-            for (int kk = 0; kk < KSTEPS; ++kk)
-                ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 16 + (lane >> 4) * 8);
+        for (int half = 0; half < 2; ++half) {
+            const int jb = j0 + half * 32;
+            // skip 32-key blocks that lie wholly after, or wholly before, what this warp's rows may see
+            const bool live = warp_has_rows && jb <= warp_hi && jb + 31 >= warp_lo;
+            float sreg[4][4];
+            if (live) {
+                qk_tile_shared_q<4>(sreg, Qw, Ks, half * 32);
+#pragma unroll
+                for (int n = 0; n < 4; ++n)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sreg[n][c] *= sc;
+                softmax_update<4>(sreg, m_run, l_run, o, jb, plo, phi);
+            }
+            if (half == 0) {
+                cp_async_wait<0>();                         // now the values are needed
+                __syncthreads();
+            }
+            if (live) pv_tile<4>(o, sreg, Vs, half * 32);
         }
-        const bf16* Kt = Ks + buf * BN * LDS;
-        const bf16* Vt = Vs + buf * BN * LDS;
-        // the warp's rows see keys up to the larger of its two thread-row limits; whole-tile skip when none
-        const int warp_hi = start + min(q_len - 1, (m0 + warp * 16 + 15) / G);
-        if (j0 <= warp_hi && m0 + warp * 16 < M) {
-            float s[BN / 8][4];
-            qk_tile<BN / 8>(s, qf, Kt, 0);
-#pragma unroll
-            for (int n = 0; n < BN / 8; ++n)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) s[n][c] *= sc;
-            softmax_update<BN / 8>(s, m_run, l_run, o, j0, plo, phi);
-            pv_tile<BN / 8>(o, s, Vt, 0);
-        }
-        __syncthreads();
-        buf ^= 1;
+        __syncthreads();                                    // everyone is done with the tiles before they are refilled
     }
-    cp_async_wait<0>();
 
     // write the rows
 #pragma unroll
@@ -528,7 +552,7 @@ __global__ void attention_combine_kernel(FastAttnArgs a) {
     }
 }
 
-constexpr size_t PORTION_SMEM = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
+constexpr size_t PORTION_SMEM = (size_t)(BM + 2 * BN) * LDS * sizeof(bf16);
 constexpr size_t DECODE_SMEM = (size_t)(16 * LDS + 4 * DSTAGES * STAGE_ELEMS) * sizeof(bf16);
 static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)4 * DSTAGES * STAGE_ELEMS * sizeof(bf16), "the merge buffer must fit the stage buffers");
 
