@@ -86,18 +86,21 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 // Load keys [j0, j0+BN) of one key/value head into a [BN][LDS] shared tile (K or V).  Keys outside
 // [lo, hi] become zeros.
+// `page_shift` is log2(page size) when that is a power of two, else -1 (then the page is found by division).
 __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* cache, const int* bt, int which, int kvh, int nkv,
-                                             int ps, int j0, int lo, int hi) {
+                                             int ps, int page_shift, int j0, int lo, int hi) {
     constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per key row
+    const size_t head_off = ((size_t)which * nkv + kvh) * ps;      // row offset of this head inside a page
+    const size_t page_rows = (size_t)2 * nkv * ps;                 // rows of a whole page (K and V, all heads)
+#pragma unroll
     for (int c = threadIdx.x; c < BN * CHUNKS; c += THREADS) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
         const int j = j0 + r;
         const bool valid = j >= lo && j <= hi;
         const bf16* src = cache;
         if (valid) {
-            const int blk = j / ps;
-            const int page = bt[blk];
-            src = cache + ((((size_t)page * 2 + which) * nkv + kvh) * ps + (j - blk * ps)) * HD + ch * 8;
+            const int blk = page_shift >= 0 ? (j >> page_shift) : (j / ps);
+            src = cache + ((size_t)bt[blk] * page_rows + head_off + (j - blk * ps)) * HD + ch * 8;
         }
         cp_async_16(dst + r * LDS + ch * 8, src, valid);
     }
@@ -145,44 +148,53 @@ __device__ __forceinline__ void pv_tile(float (&o)[DTILES][4], const float (&p)[
     }
 }
 
-// Mask, running maximum and sum for the two rows a thread holds (r0 = lane/4, r1 = r0 + 8).
-// s is scaled to base-2 exponent units on entry and holds the probabilities on exit.
+__device__ __forceinline__ float fast_exp2(float x) {     // 2^x, x <= 0 here; results below the normal range become 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Running maximum and sum for the two rows a thread holds (r0 = lane/4, r1 = r0 + 8), and the rescaling of
+// the output accumulators.  s holds raw scores (q.k) on entry and the probabilities on exit; `sc` is
+// scale * log2(e), applied inside the exponent; m is kept in those base-2 units.  MASK: keys outside
+// [plo, phi] of a row are excluded (needed only for tiles that touch the diagonal or a window's edge).
 // key index of s[n][c] is jbase + n*8 + (lane%4)*2 + (c&1); rows c<2 -> r0, c>=2 -> r1.
-template <int NT>
+template <int NT, bool MASK>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[DTILES][4],
-                                               int jbase, const int (&plo)[2], const int (&phi)[2]) {
+                                               int jbase, const int (&plo)[2], const int (&phi)[2], float sc) {
     const int lane = threadIdx.x & 31;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const int j = jbase + n * 8 + (lane & 3) * 2 + (c & 1);
-            const int r = c >> 1;
-            if (j < plo[r] || j > phi[r]) s[n][c] = -INFINITY;
-            mx[r] = fmaxf(mx[r], s[n][c]);
+            if (MASK) {
+                const int j = jbase + n * 8 + (lane & 3) * 2 + (c & 1);
+                const int r = c >> 1;
+                if (j < plo[r] || j > phi[r]) s[n][c] = -INFINITY;
+            }
+            mx[c >> 1] = fmaxf(mx[c >> 1], s[n][c]);
         }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     }
-    float corr[2], mnew[2];
+    float corr[2], ref[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        mnew[r] = fmaxf(m[r], mx[r]);
+        const float mnew = fmaxf(m[r], mx[r] * sc);
         // a row that has seen no key yet keeps m = -inf: use 0 as the reference point so that exp2 gives 0, not NaN
-        const float ref = mnew[r] == -INFINITY ? 0.0f : mnew[r];
-        corr[r] = exp2f(m[r] - ref);
-        m[r] = mnew[r];
-        mnew[r] = ref;
+        ref[r] = mnew == -INFINITY ? 0.0f : mnew;
+        corr[r] = fast_exp2(m[r] - ref[r]);
+        m[r] = mnew;
     }
     float sum[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const float e = exp2f(s[n][c] - mnew[c >> 1]);
+            const float e = fast_exp2(fmaf(s[n][c], sc, -ref[c >> 1]));
             s[n][c] = e;
             sum[c >> 1] += e;
         }
@@ -192,10 +204,13 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
         sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
         l[r] = l[r] * corr[r] + sum[r];
     }
+    // once the maxima have settled the factors are exactly 1 for the whole warp: skip the multiplications
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
 #pragma unroll
-    for (int d = 0; d < DTILES; ++d) {
-        o[d][0] *= corr[0]; o[d][1] *= corr[0];
-        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        for (int d = 0; d < DTILES; ++d) {
+            o[d][0] *= corr[0]; o[d][1] *= corr[0];
+            o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        }
     }
 }
 
@@ -283,14 +298,20 @@ __global__ void __launch_bounds__(THREADS, PORTION_BLOCKS_PER_SM) attention_port
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
     const float sc = a.scale * LOG2E;
     const bf16* Qw = Qs + warp * 16 * LDS;
+    const int ps = a.page_size;
+    const int page_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
+    // the positions of the warp's first and last row bound what its rows may see
+    const int warp_p_lo = start + min(q_len - 1, (m0 + warp * 16) / G);
     const int warp_hi = start + min(q_len - 1, (m0 + warp * 16 + 15) / G);
-    const int warp_lo = a.window > 0 ? max(0, start + (m0 + warp * 16) / G - a.window + 1) : 0;
+    const int warp_lo = a.window > 0 ? max(0, warp_p_lo - a.window + 1) : 0;
+    const int warp_lo_last = a.window > 0 ? max(0, warp_hi - a.window + 1) : 0;
     const bool warp_has_rows = m0 + warp * 16 < M;
+    const bool warp_full = m0 + warp * 16 + 15 < M;          // no row of the warp lies past the portion
 
     for (int j0 = (lo_min / BN) * BN; j0 <= hi_max; j0 += BN) {
-        load_kv_tile(Ks, a.cache, bt, 0, kvh, a.nkv, a.page_size, j0, lo_min, hi_max);
+        load_kv_tile(Ks, a.cache, bt, 0, kvh, a.nkv, ps, page_shift, j0, lo_min, hi_max);
         cp_async_commit();                                  // (the first group also carries the Q tile)
-        load_kv_tile(Vs, a.cache, bt, 1, kvh, a.nkv, a.page_size, j0, lo_min, hi_max);
+        load_kv_tile(Vs, a.cache, bt, 1, kvh, a.nkv, ps, page_shift, j0, lo_min, hi_max);
         cp_async_commit();
         cp_async_wait<1>();                                 // the keys have landed, the values may still be on their way
         __syncthreads();
@@ -302,11 +323,11 @@ __global__ void __launch_bounds__(THREADS, PORTION_BLOCKS_PER_SM) attention_port
             float sreg[4][4];
             if (live) {
                 qk_tile_shared_q<4>(sreg, Qw, Ks, half * 32);
-#pragma unroll
-                for (int n = 0; n < 4; ++n)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) sreg[n][c] *= sc;
-                softmax_update<4>(sreg, m_run, l_run, o, jb, plo, phi);
+                // a block of keys that every row of the warp sees entirely needs no mask
+                if (warp_full && jb + 31 <= warp_p_lo && jb >= warp_lo_last)
+                    softmax_update<4, false>(sreg, m_run, l_run, o, jb, plo, phi, sc);
+                else
+                    softmax_update<4, true>(sreg, m_run, l_run, o, jb, plo, phi, sc);
             }
             if (half == 0) {
                 cp_async_wait<0>();                         // now the values are needed
@@ -446,11 +467,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
             const bf16* Kt = mine + (n % DSTAGES) * STAGE_ELEMS;
             float sreg[2][4];
             qk_tile<2>(sreg, qf, Kt, 0);
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) sreg[i][c] *= sc;
-            softmax_update<2>(sreg, m_run, l_run, o, sub * SUB, plo, phi);
+            softmax_update<2, true>(sreg, m_run, l_run, o, sub * SUB, plo, phi, sc);
             pv_tile<2>(o, sreg, Kt + SUB * LDS, 0);
             __syncwarp();                                   // all lanes have read the stage before it is refilled
         }
