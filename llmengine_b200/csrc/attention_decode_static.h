@@ -19,15 +19,17 @@
  * Limits and rules
  *   - The array holds LLME_STATIC_SCRATCH_FLOATS 32-bit values (4 MiB).  Every GPU on which the
  *     library is loaded holds that much until the process exits.  A call needs
- *     n_rows * nh * splits * (HEAD_DIM + 2) values when splits > 1 (none when splits == 1); a
+ *     65536 + n_rows * nh * splits * (HEAD_DIM + 2) values when splits > 1 (none when splits == 1); a
  *     call that needs more is refused with an error message and launches nothing.
  *   - The first call on each device looks up the array's device address (once per device, with
  *     that device current).  Make that first call outside any stream capture.
  *   - All calls on a device share the one array.  Two calls whose kernels may overlap on the GPU
  *     (different streams, no ordering between them) race on it: keep calls of this entry point
  *     ordered on one stream, or order them with events.
- *   - The array keeps whatever the previous call left there.  Nothing has to start at zero: every
- *     value that the merging kernel reads is written by the same call first.
+ *   - The array keeps whatever the previous call left there.  Only its first 65536 words (ticket
+ *     counters) have to be zero when a call starts: they are zero when the library is loaded, and every
+ *     call puts back to zero the counters it used.  Every other value that a call reads it has written
+ *     itself before.
  *
  * The argument block is the one llme_attention_decode takes; its `scratch` member is ignored.
  * The library is compiled for one head size (-DHEAD_DIM=...).

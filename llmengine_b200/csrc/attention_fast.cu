@@ -9,7 +9,7 @@
 //                             form the (padded) 16-row tile, the context is split over blocks and
 //                             over the four warps of a block (each warp streams its own 16-key
 //                             sub-tiles), partial (max, sum, output) triples go to scratch memory
-//                             and attention_combine_kernel merges them.
+//                             and the block that finishes last for a head merges them.
 //
 // Both read keys and values only from the cache pages through the block table, mask by the
 // absolute position of each query (causal, optional window) and never let a cache row outside
@@ -359,19 +359,42 @@ __global__ void __launch_bounds__(THREADS, PORTION_BLOCKS_PER_SM) attention_port
 // 16-key sub-tiles w, w+4, w+8, ... of the block's share and streams them through a pipeline of its own
 // (DSTAGES sub-tiles in flight per warp, no block-wide barrier inside the loop), so that enough bytes are
 // in flight to cover the memory latency.  At the end the warps' partial results are merged in shared
-// memory; with more than one split the block's result goes to scratch memory.
+// memory; with more than one split the block's result goes to scratch memory and the last block to
+// arrive merges the splits.
 // Scratch per (request row, query head, split): HD outputs (not normalised), then max (base-2 units) and sum.
 constexpr int PART = HD + 2;
+// Scratch layout: COUNTER_WORDS ticket counters (one per (request, key/value head) of a call; they must be
+// zero before the first call and every call leaves them zero), then the partial results.
+constexpr int COUNTER_WORDS = 65536;
+__device__ __forceinline__ float* partials(const FastAttnArgs& a) { return a.scratch + COUNTER_WORDS; }
 constexpr int SUB = 16;           // keys per sub-tile
 constexpr int DSTAGES = 3;        // stage buffers per warp (two sub-tiles in flight while one is used); two blocks fit an SM
 constexpr int STAGE_ELEMS = 2 * SUB * LDS;   // K rows then V rows
 
 // One warp loads keys [j0, j0+16) (K and V) into its stage buffer; keys outside [lo, hi] become zeros.
+// When the page size is a multiple of 16 (page_shift >= 4) the 16 keys lie in one page: one look-up in the
+// block table, and every lane's addresses differ from one another only by constants.
 __device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, const int* bt, int kvh, int nkv, int ps,
                                               int page_shift, int j0, int lo, int hi) {
     const int lane = threadIdx.x & 31;
     constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per key row
     constexpr int TOTAL = SUB * CHUNKS;            // chunks of K (and as many of V)
+    if (page_shift >= 4) {
+        const int blk = j0 >> page_shift;
+        const bool any = j0 + SUB - 1 >= lo && j0 <= hi;
+        const bf16* kbase = cache;
+        if (any) kbase = cache + ((((size_t)bt[blk] * 2) * nkv + kvh) * ps + (j0 - (blk << page_shift))) * HD;
+        const size_t v_off = (size_t)nkv * ps * HD;
+#pragma unroll
+        for (int c = lane; c < TOTAL; c += 32) {
+            const int r = c / CHUNKS, ch = c - r * CHUNKS;
+            const bool valid = j0 + r >= lo && j0 + r <= hi;
+            const bf16* src = kbase + r * HD + ch * 8;
+            cp_async_16(dst + r * LDS + ch * 8, valid ? src : cache, valid);
+            cp_async_16(dst + (SUB + r) * LDS + ch * 8, valid ? src + v_off : cache, valid);
+        }
+        return;
+    }
 #pragma unroll
     for (int c = lane; c < TOTAL; c += 32) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
@@ -467,7 +490,12 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
             const bf16* Kt = mine + (n % DSTAGES) * STAGE_ELEMS;
             float sreg[2][4];
             qk_tile<2>(sreg, qf, Kt, 0);
-            softmax_update<2, true>(sreg, m_run, l_run, o, sub * SUB, plo, phi, sc);
+            // only the sub-tiles at the two ends of the visible range hold keys that must be masked
+            // (rows past the group's heads hold zero queries: finite, and never stored)
+            if (sub * SUB >= lo && sub * SUB + SUB - 1 <= p)
+                softmax_update<2, false>(sreg, m_run, l_run, o, sub * SUB, plo, phi, sc);
+            else
+                softmax_update<2, true>(sreg, m_run, l_run, o, sub * SUB, plo, phi, sc);
             pv_tile<2>(o, sreg, Kt + SUB * LDS, 0);
             __syncwarp();                                   // all lanes have read the stage before it is refilled
         }
@@ -514,7 +542,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
                 dst[d] = __float2bfloat16_rn(acc * inv);
             }
         } else {
-            float* dst = a.scratch + (((size_t)zi * a.nh + head) * a.splits + split) * PART;
+            float* dst = partials(a) + (((size_t)zi * a.nh + head) * a.splits + split) * PART;
             for (int d = lane; d < HD; d += 32) {
                 float acc = 0.0f;
 #pragma unroll
@@ -527,45 +555,51 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
             }
         }
     }
-}
+    if (a.splits == 1) return;
 
-// One warp per (request row, query head): merge the splits' partial results.  The lanes first take one
-// split each (maximum and total weight), then one output column each; the loads of a loop do not depend
-// on each other, so they are in flight together.
-__global__ void attention_combine_kernel(FastAttnArgs a) {
-    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
-    pdl_wait();                // everything below reads or writes what earlier kernels touch
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int idx = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (idx >= a.n_rows * a.nh) return;
-    const int zi = idx / a.nh, head = idx - zi * a.nh;
-    const int r = a.rows[zi];
-    const int t = a.cu_q_lens[r];
-    const float* src = a.scratch + (size_t)idx * a.splits * PART;
-    float mm = -INFINITY;
-    for (int s = lane; s < a.splits; s += 32) mm = fmaxf(mm, src[s * PART + HD]);
-    mm = warp_max(mm);
-    const float ref = mm == -INFINITY ? 0.0f : mm;
-    float ll = 0.0f;
-    for (int s = lane; s < a.splits; s += 32) ll += exp2f(src[s * PART + HD] - ref) * src[s * PART + HD + 1];
-    ll = warp_sum(ll);
-    const float inv = 1.0f / ll;
-    bf16* dst = a.out + ((size_t)t * a.nh + head) * HD;
-    float acc[(HD + 31) / 32];
+    // The block that finishes last for this (request, key/value head) merges the splits.  No block waits
+    // for another: each one publishes its partial results, takes a ticket, and only the holder of the last
+    // ticket goes on (and puts the counter back to zero for the next call).
+    __shared__ int last_block;
+    __threadfence();                                       // this block's partial results are visible device-wide
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = reinterpret_cast<int*>(a.scratch) + (size_t)zi * gridDim.y + blockIdx.y;
+        const int ticket = atomicAdd(counter, 1);
+        last_block = ticket == a.splits - 1;
+        if (last_block) *counter = 0;
+    }
+    __syncthreads();
+    if (!last_block) return;
+    __threadfence();
+    for (int row = warp; row < rows_here; row += 4) {
+        const int head = kvh * G + g0 + row;
+        const float* src = partials(a) + ((size_t)zi * a.nh + head) * a.splits * PART;
+        float mm = -INFINITY;
+        for (int s = lane; s < a.splits; s += 32) mm = fmaxf(mm, __ldcg(src + s * PART + HD));
+        mm = warp_max(mm);
+        const float ref = mm == -INFINITY ? 0.0f : mm;
+        float ll = 0.0f;
+        for (int s = lane; s < a.splits; s += 32) ll += exp2f(__ldcg(src + s * PART + HD) - ref) * __ldcg(src + s * PART + HD + 1);
+        ll = warp_sum(ll);
+        float acc[(HD + 31) / 32];
 #pragma unroll
-    for (int k = 0; k < (HD + 31) / 32; ++k) acc[k] = 0.0f;
-    for (int s = 0; s < a.splits; ++s) {
-        const float w = exp2f(src[s * PART + HD] - ref);
+        for (int k = 0; k < (HD + 31) / 32; ++k) acc[k] = 0.0f;
+        for (int s = 0; s < a.splits; ++s) {                   // fixed order: the result does not depend on which block came last
+            const float w = exp2f(__ldcg(src + s * PART + HD) - ref);
+#pragma unroll
+            for (int k = 0; k < (HD + 31) / 32; ++k) {
+                const int d = lane + 32 * k;
+                if (d < HD && w != 0.0f) acc[k] += w * __ldcg(src + s * PART + d);   // an empty split holds zeros and weight 0
+            }
+        }
+        bf16* dst = a.out + ((size_t)t * a.nh + head) * HD;
+        const float inv = 1.0f / ll;
 #pragma unroll
         for (int k = 0; k < (HD + 31) / 32; ++k) {
             const int d = lane + 32 * k;
-            if (d < HD && w != 0.0f) acc[k] += w * src[s * PART + d];      // an empty split holds zeros and weight 0
+            if (d < HD) dst[d] = __float2bfloat16_rn(acc[k] * inv);
         }
-    }
-#pragma unroll
-    for (int k = 0; k < (HD + 31) / 32; ++k) {
-        const int d = lane + 32 * k;
-        if (d < HD) dst[d] = __float2bfloat16_rn(acc[k] * inv);
     }
 }
 
@@ -588,7 +622,7 @@ LLME_API int llme_attention_head_dim() { return HD; }
 
 // Floats of scratch that the decode kernel needs for `n_rows` requests.
 LLME_API long long llme_attention_decode_scratch_floats(int n_rows, int nh, int splits) {
-    return splits <= 1 ? 0 : (long long)n_rows * nh * splits * PART;
+    return splits <= 1 ? 0 : (long long)COUNTER_WORDS + (long long)n_rows * nh * splits * PART;
 }
 
 LLME_API int llme_attention_portion(const FastAttnArgs* args, int max_q_len, cudaStream_t stream) {
@@ -625,10 +659,7 @@ LLME_API int llme_attention_decode(const FastAttnArgs* args, cudaStream_t stream
     const int chunks = (G + 15) / 16;
     if ((long long)a.nkv * chunks > 65535) LLME_REFUSE("attention: grid too large");
     dim3 grid(a.splits, a.nkv * chunks, a.n_rows);
+    if ((long long)a.n_rows * a.nkv * chunks > COUNTER_WORDS) LLME_REFUSE("attention: more than %d (request, head) pairs in one split launch", COUNTER_WORDS);
     llme_launch(attention_decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, stream, a);
-    if (a.splits > 1) {
-        const int warps = a.n_rows * a.nh;
-        llme_launch(attention_combine_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, a);
-    }
     LLME_LAUNCH_STATUS();
 }

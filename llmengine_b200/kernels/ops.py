@@ -231,7 +231,8 @@ class CudaOps:
                          num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, splits: int,
                          scratch: Optional[torch.Tensor]) -> None:
         """Tensor-core attention for the requests `rows`, each with exactly one new token; the context
-        of each is split over `splits` blocks whose partial results meet in `scratch`."""
+        of each is split over `splits` blocks whose partial results meet in `scratch`.  The first 65536
+        words of `scratch` are counters: zero before the first call, left zero by every call."""
         lib = self._fast_lib(head_dim)
         if splits > 1:
             need = self.attention_decode_scratch_floats(head_dim, rows.numel(), num_heads, splits)
@@ -240,8 +241,6 @@ class CudaOps:
                             num_kv_heads, page_size, window, scale, splits, scratch)
         rc = lib.llme_attention_decode(byref(a), self._stream())
         self._check(lib, rc, "attention_decode")
-        if splits > 1:
-            self.launches += 1
 
     def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         lib = self._lib("elementwise")

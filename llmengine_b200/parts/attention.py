@@ -122,7 +122,7 @@ class GQAttention(Part):
             scratch = None
             if splits > 1:
                 need = ops.attention_decode_scratch_floats(self.hd, n_dec, self.nh, splits)
-                scratch = rt.buffer("attention_scratch", 1, need, torch.float32, exact=True)
+                scratch = rt.buffer("attention_scratch", 1, need, torch.float32, exact=True, zero=True)   # its counters start at zero
             ops.attention_decode(rows=batch.decode_rows, splits=splits, scratch=scratch, **meta, **common)
 
     def decode_splits(self, n_requests: int, max_ctx: int) -> int:

@@ -97,10 +97,12 @@ class Runtime:
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self._tables: Dict[Any, torch.Tensor] = {}
 
-    def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype, exact: bool = False) -> torch.Tensor:
+    def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype, exact: bool = False,
+               zero: bool = False) -> torch.Tensor:
         """A [rows, cols] view of a persistent buffer: the same name gives the same memory every
         step (so captured steps can be replayed), grown only when a larger shape is asked for.
-        `exact`: the buffer is not indexed by tokens, make it only as large as asked for."""
+        `exact`: the buffer is not indexed by tokens, make it only as large as asked for.
+        `zero`: the memory is zeroed when it is allocated (not at later calls)."""
         key = (name, dtype)
         need = max(rows, 1) * cols
         buf = self._buffers.get(key)
@@ -110,7 +112,7 @@ class Runtime:
             # token-indexed buffers are made for the step's token budget at once; very wide ones
             # (logits) only as large as asked for
             cap = max(need, full) if (not exact and full * itemsize <= (256 << 20)) else need
-            buf = torch.empty(cap, dtype=dtype, device=self.device)
+            buf = (torch.zeros if zero else torch.empty)(cap, dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[: rows * cols].view(rows, cols)
 

@@ -343,6 +343,7 @@ def _run_fast(ops, case, nh, nkv, hd, page, window, q_lens, splits=None):
         sp = splits or 3
         need = ops.attention_decode_scratch_floats(hd, len(dec), nh, sp)
         scratch = torch.full((max(need, 1),), float("nan"), device=DEV)
+        scratch[:65536] = 0                       # the ticket counters start at zero; the rest may hold anything
         ops.attention_decode(rows=torch.tensor(dec, dtype=torch.int32, device=DEV), splits=sp, scratch=scratch, **common)
     return out
 

@@ -51,7 +51,7 @@ def test_static_scratch_entry_point_matches_the_regular_one():
         want = torch.full_like(case["q"], float("nan"))
         need = ops.attention_decode_scratch_floats(hd, len(ctx_lens), nh, splits)
         assert 0 < need <= capacity
-        ops.attention_decode(out=want, splits=splits, scratch=torch.empty(need, device=DEV), **common)
+        ops.attention_decode(out=want, splits=splits, scratch=torch.zeros(need, device=DEV), **common)
         # the entry point with built-in scratch: inputs and outputs only
         got = torch.full_like(case["q"], float("nan"))
         args = _FastAttnArgs(case["q"].data_ptr(), case["cache"].data_ptr(), got.data_ptr(), rows.data_ptr(),
@@ -74,7 +74,7 @@ def test_static_scratch_entry_point_matches_the_regular_one():
                         case["cu_q_lens"].data_ptr(), case["ctx_lens"].data_ptr(), case["table_rows"].data_ptr(),
                         case["block_tables"].data_ptr(), None, case["block_tables"].shape[1], 64, 128, 2, page, 0, 2,
                         1 / math.sqrt(hd))
-    assert 64 * 128 * 2 * (hd + 2) > capacity
+    assert 65536 + 64 * 128 * 2 * (hd + 2) > capacity
     rc = lib.llme_attention_decode_static(ctypes.byref(big), stream)
     assert rc == -1
     assert "scratch values" in lib.llme_last_error().decode()
