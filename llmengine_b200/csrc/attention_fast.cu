@@ -244,7 +244,6 @@ __device__ __forceinline__ void qk_tile_shared_q(float (&s)[NT][4], const bf16* 
 constexpr int PORTION_BLOCKS_PER_SM = HD <= 64 ? 6 : 4;
 
 __global__ void __launch_bounds__(THREADS, PORTION_BLOCKS_PER_SM) attention_portion_kernel(FastAttnArgs a) {
-    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     pdl_wait();                // everything below reads or writes what earlier kernels touch
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS]
@@ -338,6 +337,7 @@ __global__ void __launch_bounds__(THREADS, PORTION_BLOCKS_PER_SM) attention_port
         __syncthreads();                                    // everyone is done with the tiles before they are refilled
     }
 
+    pdl_launch_dependents();
     // write the rows
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -412,7 +412,7 @@ __device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, cons
 }
 
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs a) {
-    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    // (the next kernel is let in just before the merge below, not here: it would compete with the key/value stream)
     pdl_wait();                // everything below reads or writes what earlier kernels touch
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][LDS]
@@ -503,6 +503,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
     }
     __syncthreads();
 
+    pdl_launch_dependents();
     // merge the four warps' partial results in shared memory, in a fixed order
 #pragma unroll
     for (int i = 0; i < 2; ++i) {

@@ -45,8 +45,9 @@ inline char* llme_error_buffer() {
 // after pdl_wait(), which returns when the earlier kernel has completed.  Work that does not depend on
 // it (reading weights) may come first.  pdl_launch_dependents() lets the next kernel be scheduled early.
 // Both are no-ops for kernels launched the ordinary way.  It is off unless LLME_PDL=1 is set in the
-// environment: measured inside CUDA graphs on B200 (Qwen3-8B shape, batch 8) the decode step took 4.84 ms
-// with it and 4.57 ms without, so for now the launches are ordinary ones.
+// environment: measured inside CUDA graphs on B200 (Qwen3-8B shape, batch 8) the decode step took 5.1 ms
+// with it (6.7 ms when every kernel let its successor in at its very start) and 3.85 ms without: the
+// early-resident successors take issue slots and bandwidth from the kernel on the critical path.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

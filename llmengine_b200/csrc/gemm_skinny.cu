@@ -70,13 +70,14 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f;
 
-    pdl_launch_dependents();
-    pdl_wait();
     const int chunks = a.K / KC;                      // whole chunks; the rest of K is handled below
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     int c = warp;
+    bool first = true;
     for (; c + (UNROLL - 1) * WARPS < chunks; c += UNROLL * WARPS) {
         uint4 wa[UNROLL][2], wb[UNROLL][2], xv[UNROLL][MT][2];
+        // the weights do not depend on the kernel before this one: the first group of them is requested
+        // before waiting for it; x, which that kernel produced, only after
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = (c + u * WARPS) * KC;
@@ -84,10 +85,20 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
             for (int b = 0; b < 2; ++b) {
                 wa[u][b] = load_stream(w0 + k + b * 32);
                 wb[u][b] = load_stream(w1 + k + b * 32);
+            }
+        }
+        if (first) {
+            pdl_wait();
+            first = false;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (c + u * WARPS) * KC;
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
 #pragma unroll
                 for (int m = 0; m < MT; ++m)
                     xv[u][m][b] = xok[m] ? *reinterpret_cast<const uint4*>(xr[m] + k + b * 32) : zero;
-            }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
@@ -99,6 +110,7 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
                     mma_bf16(acc[m], wa[u][b].z, wb[u][b].z, wa[u][b].w, wb[u][b].w, xv[u][m][b].z, xv[u][m][b].w);
                 }
     }
+    if (first) pdl_wait();
     // this warp's remaining chunks, the last of which may be a partial one
     const int chunks_all = (a.K + KC - 1) / KC;
     for (; c < chunks_all; c += WARPS) {
@@ -117,6 +129,7 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
         }
     }
 
+    pdl_launch_dependents();   // only the short epilogue is left: the next kernel may move in
     // sum the warps' partial results in a fixed order and write out[token][n0 + row]
 #pragma unroll
     for (int m = 0; m < MT; ++m)
