@@ -171,8 +171,8 @@ class CacheManager:
             elif isinstance(spec, StateSpec):
                 self.state[i] = torch.zeros(self.max_requests, *spec.shape, dtype=spec.dtype, device=device)
         self.tables_dev = [torch.from_numpy(t).to(device) for t in self.tables]
-        self._staging = [torch.from_numpy(t.copy()).pin_memory() if device.type == "cuda" else torch.from_numpy(t.copy())
-                         for t in self.tables]
+        self._patch_ring = [(None, None) for _ in range(8)]
+        self._patch_next = 0
 
     def bytes_per_token(self, dtype: torch.dtype) -> int:
         size = torch.empty((), dtype=dtype).element_size()
@@ -180,16 +180,40 @@ class CacheManager:
                    if isinstance(s, PagedKVSpec) and c is None)
 
     def flush(self) -> None:
-        """Bring the device block tables and the states of newly started requests up to date."""
+        """Bring the device block tables and the states of newly started requests up to date, without
+        waiting for the device: the changed table entries travel as (position, value) pairs through a
+        small ring of pinned buffers and are scattered into the tables by the stream."""
         if not self.tables_dev:
             self._dirty = [dict() for _ in self.groups]
             self._new_slots = []
             return
         for gi, dirty in enumerate(self._dirty):
-            for slot, (lo, hi) in dirty.items():
-                self._staging[gi][slot, lo:hi] = torch.from_numpy(self.tables[gi][slot, lo:hi])
-                self.tables_dev[gi][slot, lo:hi].copy_(self._staging[gi][slot, lo:hi], non_blocking=False)
+            if not dirty:
+                continue
+            width = self.tables[gi].shape[1]
+            idx = np.concatenate([np.arange(slot * width + lo, slot * width + hi, dtype=np.int64)
+                                  for slot, (lo, hi) in dirty.items()])
+            val = self.tables[gi].reshape(-1)[idx]
             dirty.clear()
+            n = idx.size
+            ring = self._patch_ring
+            slot_i = self._patch_next % len(ring)
+            self._patch_next += 1
+            pinned, event = ring[slot_i]
+            if pinned is None or pinned.shape[1] < n:
+                pinned = torch.empty(2, max(n, 1024), dtype=torch.int64)
+                if self.tables_dev[gi].is_cuda:
+                    pinned = pinned.pin_memory()
+                event = torch.cuda.Event() if self.tables_dev[gi].is_cuda else None
+                ring[slot_i] = (pinned, event)
+            elif event is not None:
+                event.synchronize()                       # the copy that last used this buffer has been issued long ago
+            pinned[0, :n] = torch.from_numpy(idx)
+            pinned[1, :n] = torch.from_numpy(val.astype(np.int64))
+            dev = pinned[:, :n].to(self.tables_dev[gi].device, non_blocking=True)
+            if event is not None:
+                event.record()
+            self.tables_dev[gi].view(-1).index_copy_(0, dev[0], dev[1].to(torch.int32))
         for slot in self._new_slots:
             for st in self.state.values():
                 st[slot].zero_()

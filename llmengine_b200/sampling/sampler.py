@@ -58,8 +58,9 @@ class Sampler:
         self.ops, self.device, self.max_rows = ops, device, max_rows
         pin = device.type == "cuda"
         # row-wise options, packed so that one copy brings them to the device
-        self._host = torch.zeros(5, max_rows, dtype=torch.float32, pin_memory=pin)
-        self._dev = torch.zeros(5, max_rows, dtype=torch.float32, device=device)
+        self._host = torch.zeros(6, max_rows, dtype=torch.float32, pin_memory=pin)
+        self._dev = torch.zeros(6, max_rows, dtype=torch.float32, device=device)
+        self._dev_int = self._dev.view(torch.int32)          # rows 4 and 5 hold integers
         self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], draws: Sequence[int],
@@ -77,12 +78,12 @@ class Sampler:
             h[3, r] = p.repetition_penalty
         hi = self._host.view(torch.int32).numpy()
         for r, p in enumerate(params):
-            hi[4, r] = (p.top_k << 1) | (1 if p.greedy else 0)
+            hi[4, r] = 1 if p.greedy else 0
+            hi[5, r] = p.top_k
         self._dev.copy_(self._host, non_blocking=True)
         dev = self._dev
-        packed = dev[4, :R].view(torch.int32)
-        greedy = packed & 1
-        top_k = packed >> 1
+        greedy = self._dev_int[4, :R]
+        top_k = self._dev_int[5, :R]
         if histories is not None and any(p.repetition_penalty != 1.0 for p in params):
             rows, toks, counts = [], [], []
             for r, (p, hist) in enumerate(zip(params, histories)):
@@ -93,7 +94,7 @@ class Sampler:
                 pairs = torch.tensor([rows, toks, counts], dtype=torch.int32).to(self.device)
                 self.ops.repetition_penalty(logits, pairs[0], pairs[1], pairs[2], dev[3, :R].contiguous())
         out = self._out[:R]
-        self.ops.sample(logits, greedy=greedy.contiguous(), temperature=dev[0, :R], top_k=top_k.contiguous(),
+        self.ops.sample(logits, greedy=greedy, temperature=dev[0, :R], top_k=top_k,
                         top_p=dev[1, :R], u=dev[2, :R], out=out)
         return out
 
