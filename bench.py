@@ -350,7 +350,7 @@ def main() -> int:
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         e2e = {"value": round(args.batch * args.steps / dt, 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": int(eng._meta_len * 4 + llm.sampler._host.numel() * 4),
+               "h2d_bytes_per_step": int(eng._meta_len * 4 + llm.sampler._hosts[0].numel() * 4),
                "d2h_bytes_per_step": int(args.batch * 4)}
     clocks.stop()
 

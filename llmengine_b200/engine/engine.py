@@ -194,12 +194,22 @@ class Engine:
             decode_rows=view("decode_rows", len(dec)), portion_rows=view("portion_rows", len(por)), groups=groups)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], end: Sequence[Hashable] = ()) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], end: Sequence[Hashable] = (),
+             device_tokens: Optional[tuple] = None) -> Optional[torch.Tensor]:
         """Run the entries' tokens as one batch.  Returns 32-bit logits [wanted, vocab] on the device,
         in the order of the entries and of their `want` lists (None if nothing is wanted); the tensor
         is overwritten by the next step.  Requests named in `end` give back what they hold after the
-        step.  A request is created by its first entry.  A refused batch changes nothing."""
+        step.  A request is created by its first entry.  A refused batch changes nothing.
+
+        `device_tokens = (tensor, indices)`: for a step of single tokens, entry r's token is not the
+        (placeholder) value in the entry but `tensor[indices[r]]`, an int32 tensor on the device (the
+        output of the previous step's sampler): the step can be launched before the host has seen it."""
         entries = [e for e in entries if len(e.tokens) > 0]
+        fast = self._decode_step(entries, end, device_tokens)
+        if fast is not NotImplemented:
+            return fast
+        if device_tokens is not None:
+            raise StepError("tokens on the device are only taken for a step of single tokens of live requests")
         seen = set()
         total = 0
         for e in entries:
@@ -255,6 +265,92 @@ class Engine:
             for e, s in zip(entries, starts):
                 self.cache.advance(e.request, s + len(e.tokens))
             self.steps += 1
+        for r in end:
+            self.cache.free_request(r)
+        return logits
+
+    @property
+    def takes_device_tokens(self) -> bool:
+        """Whether `step(..., device_tokens=...)` is served (one cache group that keeps all positions)."""
+        return len(self.cache.groups) == 1 and not self.cache.groups[0].window
+
+    def _decode_step(self, entries, end, device_tokens=None):
+        """The common case made cheap on the host: every entry is one token of a live request that wants
+        its logits.  Same checks and same effects as the general path, computed with whole-batch array
+        operations instead of per-request ones.  Returns NotImplemented when the batch is of another kind."""
+        R = len(entries)
+        if R == 0 or R > self._R_cap or len(self.cache.groups) != 1 or self.cache.groups[0].window:
+            return NotImplemented
+        reqs = self.cache.requests
+        states = []
+        for e in entries:
+            st = reqs.get(e.request)
+            if st is None or len(e.tokens) != 1 or len(e.want) != 1 or e.want[0] != 0:
+                return NotImplemented
+            states.append(st)
+        if len({id(st) for st in states}) != R:
+            return NotImplemented                          # a request twice: let the general path refuse it
+        for r in end:
+            if r not in reqs:
+                return NotImplemented
+        toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
+        if toks.min() < 0 or toks.max() >= self.vocab_size:
+            return NotImplemented
+        lengths = np.fromiter((st.length for st in states), dtype=np.int64, count=R)
+        if lengths.max() + 1 > self.max_model_len:
+            return NotImplemented
+        slots = np.fromiter((st.slot for st in states), dtype=np.int64, count=R)
+        g = self.cache.groups[0]
+        ps = g.page_size
+        grow = np.nonzero(lengths % ps == 0)[0]            # these requests step onto a new page
+        if grow.size:
+            if any(len(states[i].blocks[0]) * ps <= lengths[i] for i in grow):
+                need = sum(1 for i in grow if len(states[i].blocks[0]) * ps <= lengths[i])
+                if need > g.pool.free_count:
+                    return NotImplemented                  # the general path raises the error and undoes nothing
+                for i in grow:
+                    self.cache.reserve(entries[i].request, int(lengths[i]) + 1)
+        i = self.steps & 1
+        if self._staging_ev[i] is not None and self._staging_used[i]:
+            self._staging_ev[i].synchronize()
+        h, off = self._staging_np[i], self._off
+        ar = np.arange(R, dtype=np.int32)
+        h[off["token_ids"]][:R] = toks
+        h[off["positions"]][:R] = lengths
+        h[off["token_request"]][:R] = slots
+        h[off["slot_mapping0"]][:R] = self.cache.tables[0][slots, lengths // ps].astype(np.int64) * ps + lengths % ps
+        h[off["logit_rows"]][:R] = ar
+        h[off["cu_q_lens"]][:R + 1] = np.arange(R + 1, dtype=np.int32)
+        h[off["ctx_lens"]][:R] = lengths + 1
+        h[off["state_slots"]][:R] = slots
+        h[off["first_portion"]][:R] = lengths == 0
+        h[off["decode_rows"]][:R] = ar
+        if device_tokens is not None:
+            h[off["portion_rows"]][:R] = np.asarray(device_tokens[1], dtype=np.int32)   # unused in a decode step: carries the indices
+        self._meta_dev.copy_(self._staging[i], non_blocking=True)
+        if self._staging_ev[i] is not None:
+            self._staging_ev[i].record()
+            self._staging_used[i] = True
+        d = self._meta_dev
+
+        def view(name: str, n: int) -> torch.Tensor:
+            s = off[name]
+            return d[s.start:s.start + n]
+
+        if device_tokens is not None:
+            torch.index_select(device_tokens[0], 0, view("portion_rows", R), out=view("token_ids", R))
+        group = GroupView(ps, 0, self.cache.tables_dev[0], view("slot_mapping0", R), g.max_blocks)
+        batch = StepBatch(
+            num_tokens=R, num_requests=R, q_lens=[1] * R, start_positions=lengths.tolist(),
+            token_ids=view("token_ids", R), positions=view("positions", R), token_request=view("token_request", R),
+            cu_q_lens=view("cu_q_lens", R + 1), ctx_lens=view("ctx_lens", R), state_slots=view("state_slots", R),
+            first_portion=view("first_portion", R), logit_rows=view("logit_rows", R),
+            decode_rows=view("decode_rows", R), portion_rows=view("portion_rows", 0), groups=[group])
+        self.cache.flush()
+        logits = self._forward(batch)
+        for st in states:
+            st.length += 1
+        self.steps += 1
         for r in end:
             self.cache.free_request(r)
         return logits

@@ -58,10 +58,16 @@ class Sampler:
         self.ops, self.device, self.max_rows = ops, device, max_rows
         pin = device.type == "cuda"
         # row-wise options, packed so that one copy brings them to the device
-        self._host = torch.zeros(6, max_rows, dtype=torch.float32, pin_memory=pin)
+        # the options travel through pinned buffers used in turn; an event tells when a buffer's copy has run,
+        # so that a later call (steps may be queued without waiting for each other) never overwrites it early
+        self._hosts = [torch.zeros(6, max_rows, dtype=torch.float32, pin_memory=pin) for _ in range(4)]
+        self._host_events = [None] * 4
+        self._host_turn = 0
         self._dev = torch.zeros(6, max_rows, dtype=torch.float32, device=device)
         self._dev_int = self._dev.view(torch.int32)          # rows 4 and 5 hold integers
-        self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        # two output buffers used in turn: the tokens of one step stay readable while the next step samples
+        self._outs = [torch.zeros(max_rows, dtype=torch.int32, device=device) for _ in range(2)]
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], draws: Sequence[int],
                histories: Optional[Sequence[Dict[int, int]]] = None) -> torch.Tensor:
@@ -70,17 +76,25 @@ class Sampler:
         Returns int32 [R] on the device."""
         R = logits.shape[0]
         assert R == len(params) == len(draws) and R <= self.max_rows
-        h = self._host.numpy()
+        k = self._host_turn
+        self._host_turn = (k + 1) % len(self._hosts)
+        if self._host_events[k] is not None:
+            self._host_events[k].synchronize()
+        host = self._hosts[k]
+        h = host.numpy()
         for r, (p, d) in enumerate(zip(params, draws)):
             h[0, r] = p.temperature
             h[1, r] = p.top_p
-            h[2, r] = uniform(p.seed, d)
+            h[2, r] = 0.5 if p.greedy else uniform(p.seed, d)
             h[3, r] = p.repetition_penalty
-        hi = self._host.view(torch.int32).numpy()
+        hi = host.view(torch.int32).numpy()
         for r, p in enumerate(params):
             hi[4, r] = 1 if p.greedy else 0
             hi[5, r] = p.top_k
-        self._dev.copy_(self._host, non_blocking=True)
+        self._dev.copy_(host, non_blocking=True)
+        if self.device.type == "cuda":
+            self._host_events[k] = torch.cuda.Event()
+            self._host_events[k].record()
         dev = self._dev
         greedy = self._dev_int[4, :R]
         top_k = self._dev_int[5, :R]
@@ -93,7 +107,8 @@ class Sampler:
             if rows:
                 pairs = torch.tensor([rows, toks, counts], dtype=torch.int32).to(self.device)
                 self.ops.repetition_penalty(logits, pairs[0], pairs[1], pairs[2], dev[3, :R].contiguous())
-        out = self._out[:R]
+        self._turn ^= 1
+        out = self._outs[self._turn][:R]
         self.ops.sample(logits, greedy=greedy, temperature=dev[0, :R], top_k=top_k,
                         top_p=dev[1, :R], u=dev[2, :R], out=out)
         return out
