@@ -1,0 +1,536 @@
+// Paged causal attention for prompt portions on the tcgen05 tensor cores of sm_100a (bfloat16, head size
+// HEAD_DIM = 64 or 128, compiled per head size like attention_fast.cu).
+//
+// A block serves one request, one key/value head and 128 rows, a row being a (token, query head of the
+// group) pair.  Keys and values stream through shared memory 128 at a time:
+//
+//   warp 0      producer: TMA loads of the Q tile (a 3-D box: tokens x heads of the group x 64 columns) and,
+//               page by page through the block table, of the K and V tiles (128-byte swizzle, two stages
+//               each).  A page that holds keys beyond what the tile may see is copied by hand instead, with
+//               those rows zeroed, so that stale memory (NaN included) never reaches the tensor cores.
+//   warp 1      issues the matrix instructions: S = Q K^T (128 x 128 x HEAD_DIM) into one of two score
+//               buffers in tensor memory, and O_tile = P V (128 x HEAD_DIM x 128) into one of two output
+//               buffers; V is read as an MN-major operand, exactly as it lies in the cache.
+//   warps 2..5  one row per thread: read S from tensor memory (tcgen05.ld), mask by absolute position, keep the
+//               running maximum and sum in 32-bit, write the probabilities as bfloat16 into the swizzled P
+//               tile, and fold each O_tile into the row's output accumulator, which lives in registers.
+//
+// The score of tile i+1 is computed while the softmax of tile i runs, and P V of tile i while the softmax of
+// tile i+1 runs.  Every mbarrier wait is bounded; a wait that gives up sets an error flag (read with
+// llme_attention_tc_status()), and the block drains its copies, frees its tensor memory and returns.
+//
+// Reference counterpart: flash_sdpa_tiled_kernel (src/runtime/kernels/cuda_kernels.cu:558-645): one block per
+// query row, scalar FMA, keys of the same launch only.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=64 or -DHEAD_DIM=128"
+#endif
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "HEAD_DIM must be 64 or 128");
+
+LLME_API const char* llme_last_error() { return llme_error_buffer(); }
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int HD = HEAD_DIM;
+constexpr int HALVES = HD / 64;        // 64-column (128-byte) halves of a row
+constexpr int BM = 128;                // rows per block
+constexpr int BN = 128;                // keys per tile
+constexpr int THREADS = 192;
+constexpr int HALF_BYTES = 128 * 128;  // a [128 rows x 64 columns] bfloat16 tile with 128-byte rows
+constexpr int TILE_BYTES = HALVES * HALF_BYTES;
+constexpr unsigned WAIT_LIMIT = 1u << 20;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ int g_status = 0;
+
+struct TcAttnArgs {
+    bf16* out;                   // [T, nh, HD]
+    const bf16* cache;           // [pages][K|V][nkv][page_size][HD]
+    const int* rows;             // [n_rows] batch rows (requests) this launch serves
+    const int* cu_q_lens;        // [R+1]
+    const int* ctx_lens;         // [R] cached length after this step
+    const int* table_rows;       // [R] row of block_tables of each request
+    const int* block_tables;     // [*, max_blocks]
+    int max_blocks, n_rows, nh, nkv, page_size, window;
+    float scale;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag, int where) {
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = where;
+    atomicCAS(&g_status, 0, where);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+
+// K-major operand with 128-byte rows and the 128-byte swizzle (Q, K, P): eight rows form a 1024-byte group.
+__device__ __forceinline__ unsigned long long desc_k_major(const void* tile) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// MN-major operand (V as it lies in the cache: one key per 128-byte row, 64 columns of the head per row):
+// the 64-column chunks of the N side lie HALF_BYTES apart (leading byte offset), groups of eight keys
+// 1024 bytes apart (stride byte offset).
+__device__ __forceinline__ unsigned long long desc_mn_major(const void* tile) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)(HALF_BYTES >> 4) << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// kind::f16 instruction descriptor: D = F32, A = B = BF16, A K-major, B K-major (b_mn = 0) or MN-major (1).
+__host__ __device__ constexpr unsigned idesc(int M, int N, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)b_mn << 16) | ((unsigned)(N >> 3) << 17) | ((unsigned)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned id, unsigned acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned addr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct Barriers {
+    unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
+    unsigned long long s_full[2], s_empty[2], p_full, p_empty, o_full[2], o_empty[2];
+    unsigned tmem_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, TcAttnArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_tile = smem;                              // HALVES x [128 rows x 128 B]
+    unsigned char* k_tiles = q_tile + TILE_BYTES;              // 2 stages
+    unsigned char* v_tiles = k_tiles + 2 * TILE_BYTES;         // 2 stages
+    unsigned char* p_tile = v_tiles + 2 * TILE_BYTES;          // 2 x [128 rows x 64 keys]
+    Barriers* bar = reinterpret_cast<Barriers*>(p_tile + 2 * HALF_BYTES);
+    volatile int* abort_flag = &bar->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = a.rows[blockIdx.z];
+    const int kvh = blockIdx.y;
+    const int G = a.nh / a.nkv;
+    const int q0 = a.cu_q_lens[r];
+    const int q_len = a.cu_q_lens[r + 1] - q0;
+    const int M = q_len * G;
+    const int m0 = ((M + BM - 1) / BM - 1 - (int)blockIdx.x) * BM;     // the tiles with the most keys start first
+    if (m0 < 0) return;
+    const int start = a.ctx_lens[r] - q_len;
+    const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
+    const int ps = a.page_size;
+    const int t_lo = m0 / G, t_hi = min(q_len - 1, (m0 + BM - 1) / G);
+    const int hi_max = start + t_hi;                                  // last key any row of the tile sees
+    const int lo_min = a.window > 0 ? max(0, start + t_lo - a.window + 1) : 0;
+    const int tile_first = lo_min / BN, tile_last = hi_max / BN;
+    const int n_tiles = tile_last - tile_first + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bar->q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bar->k_full[s], 1); mbar_init(&bar->k_empty[s], 1);
+            mbar_init(&bar->v_full[s], 1); mbar_init(&bar->v_empty[s], 1);
+            mbar_init(&bar->s_full[s], 1); mbar_init(&bar->s_empty[s], 4);
+            mbar_init(&bar->o_full[s], 1); mbar_init(&bar->o_empty[s], 4);
+        }
+        mbar_init(&bar->p_full, 4);
+        mbar_init(&bar->p_empty, 1);
+        bar->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // the value tiles start as zeros: rows that are never loaded (before a window, past the last key) must not be NaN
+    for (int i = threadIdx.x; i < 2 * TILE_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(v_tiles)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)), "r"(512u));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = bar->tmem_base;
+    const unsigned tmem_s[2] = {tmem, tmem + 128};
+    const unsigned tmem_o[2] = {tmem + 256, tmem + 256 + 128};
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            mbar_expect_tx(&bar->q_full, TILE_BYTES);
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_3d(q_tile + h * HALF_BYTES, &map_q, h * 64, kvh * G, q0 + t_lo, &bar->q_full);
+        }
+        const int rows_per_box = ps < BN ? ps : BN;            // rows one TMA load of the cache brings
+        bool ok = true;
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int s = i & 1, round = i >> 1;
+            const int j0 = (tile_first + i) * BN;
+            for (int which = 0; which < 2 && ok; ++which) {       // keys, then values
+                unsigned long long* empty = which ? &bar->v_empty[s] : &bar->k_empty[s];
+                unsigned long long* full = which ? &bar->v_full[s] : &bar->k_full[s];
+                unsigned char* tile = (which ? v_tiles : k_tiles) + s * TILE_BYTES;
+                ok = mbar_wait(empty, (round & 1) ^ 1, abort_flag, 10 + which) && !*abort_flag;
+                if (!ok) break;
+                // First the boxes that straddle an edge of the visible range: they are copied by hand, visible
+                // rows only, the rest zeroed.  Then, after those writes are published, one lane arms the barrier
+                // and starts the TMA loads of the boxes that are needed whole.
+                unsigned tx = 0;
+                for (int b = 0; b < BN; b += rows_per_box) {
+                    const int ja = j0 + b, jb = ja + rows_per_box - 1;
+                    if (jb < lo_min || ja > hi_max) continue;                 // nothing of it is needed
+                    if (ja >= lo_min && jb <= hi_max) {
+                        tx += (unsigned)(HALVES * rows_per_box * 128);
+                        continue;
+                    }
+                    const int blk = ja / ps;
+                    const long long row0 = (((long long)bt[blk] * 2 + which) * a.nkv + kvh) * ps + (ja - blk * ps);
+                    for (int c = lane; c < rows_per_box * (HD / 8); c += 32) {
+                        const int rr = c / (HD / 8), ch = c % (HD / 8);
+                        const int j = ja + rr;
+                        uint4 v = make_uint4(0, 0, 0, 0);
+                        if (j >= lo_min && j <= hi_max) v = *reinterpret_cast<const uint4*>(a.cache + (row0 + rr) * HD + ch * 8);
+                        const int h = ch >> 3, q = ch & 7, row = b + rr;
+                        *reinterpret_cast<uint4*>(tile + h * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) = v;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_expect_tx(full, tx);
+                    for (int b = 0; b < BN; b += rows_per_box) {
+                        const int ja = j0 + b, jb = ja + rows_per_box - 1;
+                        if (!(ja >= lo_min && jb <= hi_max)) continue;
+                        const int blk = ja / ps;
+                        const long long row0 = (((long long)bt[blk] * 2 + which) * a.nkv + kvh) * ps + (ja - blk * ps);
+                        for (int h = 0; h < HALVES; ++h)
+                            tma_load_2d(tile + h * HALF_BYTES + b * 128, &map_kv, h * 64, (int)row0, full);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        if (*abort_flag) {
+            // gave up somewhere: give the copies that are still in flight time to land before the block exits
+            for (int i = 0; i < 200; ++i) __nanosleep(5000);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ matrix instructions
+        if (lane == 0) {
+            constexpr unsigned id_s = idesc(BM, BN, 0);
+            constexpr unsigned id_o = idesc(BM, HD, 1);
+            bool ok = mbar_wait(&bar->q_full, 0, abort_flag, 20);
+            auto issue_s = [&](int i) {
+                const int s = i & 1, round = i >> 1;
+                ok = ok && mbar_wait(&bar->k_full[s], round & 1, abort_flag, 21);
+                ok = ok && mbar_wait(&bar->s_empty[s], (round & 1) ^ 1, abort_flag, 22);
+                if (!ok) return;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) {
+                    const unsigned long long dq = desc_k_major(q_tile + h * HALF_BYTES);
+                    const unsigned long long dk = desc_k_major(k_tiles + s * TILE_BYTES + h * HALF_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma(tmem_s[s], dq + 2 * k, dk + 2 * k, id_s, (h > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&bar->k_empty[s]);
+                umma_commit(&bar->s_full[s]);
+            };
+            auto issue_o = [&](int i) {
+                const int s = i & 1, round = i >> 1;
+                ok = ok && mbar_wait(&bar->p_full, i & 1, abort_flag, 23);
+                ok = ok && mbar_wait(&bar->v_full[s], round & 1, abort_flag, 24);
+                ok = ok && mbar_wait(&bar->o_empty[s], (round & 1) ^ 1, abort_flag, 25);
+                if (!ok) return;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned long long dv = desc_mn_major(v_tiles + s * TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    // P: 16 keys = 32 bytes further inside the 64-key half; V: 16 keys = two 1024-byte groups further
+                    const unsigned long long dp = desc_k_major(p_tile + (kk >> 2) * HALF_BYTES) + 2 * (kk & 3);
+                    umma(tmem_o[s], dp, dv + (unsigned long long)(kk * (2048 >> 4)), id_o, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&bar->v_empty[s]);
+                umma_commit(&bar->p_empty);
+                umma_commit(&bar->o_full[s]);
+            };
+            if (ok) issue_s(0);
+            for (int i = 1; i < n_tiles && ok; ++i) {
+                issue_s(i);
+                issue_o(i - 1);
+            }
+            if (ok) issue_o(n_tiles - 1);
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax, accumulation, output
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                 // this thread's row of the tile
+        const int m = m0 + row;
+        const bool row_ok = m < M;
+        const int p = start + min(m, M - 1) / G;             // its position
+        const int phi = row_ok ? p : -1;
+        const int plo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+        const unsigned lane_off = (unsigned)(quarter * 32) << 16;
+        const float sc = a.scale * LOG2E;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int s = i & 1, round = i >> 1;
+            const int j0 = (tile_first + i) * BN;
+            ok = mbar_wait(&bar->s_full[s], round & 1, abort_flag, 30);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // pass 1: the row's maximum over the tile
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float v[32];
+                tmem_ld32(tmem_s[s] + lane_off + (unsigned)c, v);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int j = j0 + c + e;
+                    if (j >= plo && j <= phi) mx = fmaxf(mx, v[e]);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx * sc);
+            const float ref = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = fast_exp2(m_run - ref);
+            m_run = m_new;
+            // the P tile is free once P V of the tile before has read it
+            ok = mbar_wait(&bar->p_empty, (i & 1) ^ 1, abort_flag, 31);
+            if (!ok) break;
+            // pass 2: probabilities, their sum, and the bfloat16 P tile (row `row`, 16-byte chunk q at q ^ (row % 8))
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float v[32];
+                tmem_ld32(tmem_s[s] + lane_off + (unsigned)c, v);
+                unsigned packed[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int j = j0 + c + e;
+                    const float e0 = (j >= plo && j <= phi) ? fast_exp2(fmaf(v[e], sc, -ref)) : 0.0f;
+                    const float e1 = (j + 1 >= plo && j + 1 <= phi) ? fast_exp2(fmaf(v[e + 1], sc, -ref)) : 0.0f;
+                    sum += e0 + e1;
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
+                    packed[e >> 1] = *reinterpret_cast<unsigned*>(&hh);
+                }
+                unsigned char* half = p_tile + (c >> 6) * HALF_BYTES + row * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int q = ((c & 63) >> 3) + q4;          // chunk index within the 64-key half
+                    *reinterpret_cast<uint4*>(half + ((q ^ (row & 7)) << 4)) =
+                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+            }
+            l_run = l_run * corr + sum;
+            // S has been read and P written: tell the matrix warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bar->s_empty[s]);
+                mbar_arrive(&bar->p_full);
+            }
+            // fold the tile before into the accumulator (it is at the scale of the maximum before this tile),
+            // then bring the accumulator to the new scale
+            if (i > 0) {
+                const int sp = (i - 1) & 1;
+                ok = mbar_wait(&bar->o_full[sp], ((i - 1) >> 1) & 1, abort_flag, 32);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    float v[32];
+                    tmem_ld32(tmem_o[sp] + lane_off + (unsigned)c, v);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[c + e] = (o[c + e] + v[e]) * corr;
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar->o_empty[sp]);
+            }
+        }
+        if (ok) {
+            const int sp = (n_tiles - 1) & 1;
+            ok = mbar_wait(&bar->o_full[sp], ((n_tiles - 1) >> 1) & 1, abort_flag, 33);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float inv = 1.0f / l_run;
+                bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD;
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    float v[32];
+                    tmem_ld32(tmem_o[sp] + lane_off + (unsigned)c, v);
+                    if (row_ok) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 pk;
+                            unsigned* pw = reinterpret_cast<unsigned*>(&pk);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int d = c + q4 * 8 + 2 * e;
+                                __nv_bfloat162 hh = __floats2bfloat162_rn((o[d] + v[q4 * 8 + 2 * e]) * inv, (o[d + 1] + v[q4 * 8 + 2 * e + 1]) * inv);
+                                pw[e] = *reinterpret_cast<unsigned*>(&hh);
+                            }
+                            *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+constexpr size_t SMEM_BYTES = 1024 + (size_t)5 * TILE_BYTES + 2 * HALF_BYTES + sizeof(Barriers) + 64;
+static_assert(SMEM_BYTES <= 232448, "the block's shared memory must fit an SM");
+
+}  // namespace
+
+LLME_API int llme_attention_tc_head_dim() { return HD; }
+
+// Whether this kernel takes the problem: a page size that divides 128 and is at least 8 (a TMA box of whole
+// pages with whole swizzle groups), and a group size (query heads per key/value head) that divides 128.
+LLME_API int llme_attention_tc_supports(int nh, int nkv, int page_size) {
+    if (nkv <= 0 || nh % nkv) return 0;
+    const int G = nh / nkv;
+    return page_size >= 8 && (page_size <= 128 ? 128 % page_size == 0 : page_size % 128 == 0) && 128 % G == 0 && G <= 128;
+}
+
+// q, out [T, nh, HD] bfloat16 (q_tokens = T rows in all); the other arguments as for the portion kernel of
+// attention_fast.cu.  total_cache_rows = pages * 2 * nkv * page_size.
+LLME_API int llme_attention_tc(const void* q, long long q_tokens, long long total_cache_rows, const TcAttnArgs* args,
+                               int max_q_len, cudaStream_t stream) {
+    const TcAttnArgs& a = *args;
+    if (a.n_rows <= 0 || max_q_len <= 0) return 0;
+    if (!q || !a.out || !a.cache || !a.rows || !a.cu_q_lens || !a.ctx_lens || !a.table_rows || !a.block_tables)
+        LLME_REFUSE("attention_tc: null pointer");
+    if (!llme_attention_tc_supports(a.nh, a.nkv, a.page_size)) LLME_REFUSE("attention_tc: %d/%d heads with pages of %d are not supported", a.nh, a.nkv, a.page_size);
+    if (a.n_rows > 65535 || a.nkv > 65535) LLME_REFUSE("attention_tc: grid too large");
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) LLME_REFUSE("attention_tc: cuTensorMapEncodeTiled is not available in this driver");
+    const int G = a.nh / a.nkv;
+    alignas(64) CUtensorMap mq, mkv;
+    {   // q as [token][head][column]; a box is 128/G tokens x G heads x 64 columns = 128 rows of 128 bytes
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)a.nh, (cuuint64_t)q_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)a.nh * HD * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(BM / G)};
+        cuuint32_t es[3] = {1, 1, 1};
+        CUresult r = enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) LLME_REFUSE("attention_tc: cuTensorMapEncodeTiled (q) failed with code %d", (int)r);
+    }
+    {   // the cache as rows of HD columns; a box is one page (or 128 rows of a larger page) x 64 columns
+        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)total_cache_rows};
+        cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)(a.page_size < BN ? a.page_size : BN)};
+        cuuint32_t es[2] = {1, 1};
+        CUresult r = enc(&mkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(a.cache), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) LLME_REFUSE("attention_tc: cuTensorMapEncodeTiled (cache) failed with code %d", (int)r);
+    }
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) LLME_REFUSE("attention_tc: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    const long long tiles = ((long long)max_q_len * G + BM - 1) / BM;
+    if (tiles > 2147483647LL) LLME_REFUSE("attention_tc: grid too large");
+    dim3 grid((unsigned)tiles, a.nkv, a.n_rows);
+    attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(mq, mkv, a);
+    LLME_LAUNCH_STATUS();
+}
+
+LLME_API int llme_attention_tc_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return v;
+}

@@ -407,6 +407,10 @@ class Engine:
 
     def check_kernels(self) -> None:
         """Raise if a bounded wait inside a kernel ever gave up (synchronises the device)."""
-        status = self.ops.linear_tc_status() if hasattr(self.ops, "linear_tc_status") and "gemm_tcgen05" in getattr(self.ops, "_libs", {}) else 0
+        libs = getattr(self.ops, "_libs", {})
+        status = self.ops.linear_tc_status() if "gemm_tcgen05" in libs else 0
+        for key in libs:
+            if key.startswith("attention_tc@HEAD_DIM="):
+                status = status or self.ops.attention_tc_status(int(key.split("=")[1]))
         if status:
             raise RuntimeError(f"a tcgen05 kernel gave up waiting (code {status}): its results are not valid")

@@ -32,6 +32,8 @@ SOURCES: Dict[str, str] = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     # compiled per head size: ask for "attention_fast@HEAD_DIM=128"
     "attention_fast": "attention_fast.cu",
+    # the tcgen05 portion kernel, per head size (64 or 128): "attention_tc@HEAD_DIM=128"
+    "attention_tc": "attention_tc.cu",
     # the same kernels with built-in scratch memory: "attention_decode_static@HEAD_DIM=128"
     "attention_decode_static": "attention_decode_static.cu",
 }
@@ -43,6 +45,7 @@ INCLUDES: Dict[str, List[str]] = {"attention_decode_static": ["attention_fast.cu
 VARIANTS: Dict[str, List[str]] = {
     "attention_fast": ["attention_fast@HEAD_DIM=64", "attention_fast@HEAD_DIM=128"],
     "attention_decode_static": ["attention_decode_static@HEAD_DIM=128"],
+    "attention_tc": ["attention_tc@HEAD_DIM=64", "attention_tc@HEAD_DIM=128"],
 }
 
 NVCC_FLAGS = [

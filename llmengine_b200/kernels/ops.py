@@ -71,6 +71,15 @@ class _FastAttnArgs(Structure):
     ]
 
 
+class _TcAttnArgs(Structure):
+    _fields_ = [
+        ("out", c_void_p), ("cache", c_void_p), ("rows", c_void_p), ("cu_q_lens", c_void_p), ("ctx_lens", c_void_p),
+        ("table_rows", c_void_p), ("block_tables", c_void_p),
+        ("max_blocks", c_int), ("n_rows", c_int), ("nh", c_int), ("nkv", c_int), ("page_size", c_int),
+        ("window", c_int), ("scale", c_float),
+    ]
+
+
 class _SampleArgs(Structure):
     _fields_ = [
         ("logits", c_void_p), ("ld", c_longlong), ("rows", c_int), ("vocab", c_int),
@@ -223,6 +232,34 @@ class CudaOps:
                             num_kv_heads, page_size, window, scale)
         rc = lib.llme_attention_portion(byref(a), c_int(max_q_len), self._stream())
         self._check(lib, rc, "attention_portions")
+
+    def tc_attention_supports(self, head_dim: int, dtype: torch.dtype, num_heads: int, num_kv_heads: int,
+                              page_size: int) -> bool:
+        """Whether the tcgen05 portion kernel takes this shape (head size 64 or 128, pages of 8..128 that
+        divide 128 or multiples of 128, a group size that divides 128)."""
+        if not (self.use_tcgen05 and dtype == torch.bfloat16 and head_dim in (64, 128)):
+            return False
+        g = num_heads // num_kv_heads
+        pages_ok = page_size >= 8 and (128 % page_size == 0 if page_size <= 128 else page_size % 128 == 0)
+        return pages_ok and 128 % g == 0
+
+    def attention_portions_tc(self, *, q, cache, out, rows, cu_q_lens, ctx_lens, table_rows, block_tables,
+                              num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                              scale: float, max_q_len: int) -> None:
+        """The portion attention on the tcgen05 tensor cores (TMA-fed, scores and outputs in tensor memory)."""
+        lib = self._lib(f"attention_tc@HEAD_DIM={head_dim}")
+        assert q.dtype == cache.dtype == out.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous()
+        assert cache.is_contiguous() and block_tables.is_contiguous()
+        a = _TcAttnArgs(out.data_ptr(), cache.data_ptr(), rows.data_ptr(), cu_q_lens.data_ptr(), ctx_lens.data_ptr(),
+                        table_rows.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], rows.numel(), num_heads,
+                        num_kv_heads, page_size, window, scale)
+        total_rows = cache.shape[0] * cache.shape[1] * cache.shape[2] * cache.shape[3]
+        rc = lib.llme_attention_tc(c_void_p(q.data_ptr()), c_longlong(q.shape[0]), c_longlong(total_rows), byref(a),
+                                   c_int(max_q_len), self._stream())
+        self._check(lib, rc, "attention_tc")
+
+    def attention_tc_status(self, head_dim: int) -> int:
+        return int(self._lib(f"attention_tc@HEAD_DIM={head_dim}").llme_attention_tc_status())
 
     def attention_decode_scratch_floats(self, head_dim: int, n_rows: int, num_heads: int, splits: int) -> int:
         return int(self._fast_lib(head_dim).llme_attention_decode_scratch_floats(c_int(n_rows), c_int(num_heads), c_int(splits)))

@@ -102,7 +102,8 @@ class GQAttention(Part):
     def attend(self, q, kv, out, batch, group) -> None:
         """Attention of every token of the batch over its request's cache.  bfloat16 with head sizes
         the tensor-core kernels are built for: requests with one new token go to the split-context
-        decode kernel, the others to the portion kernel.  Everything else (32-bit, other head sizes,
+        decode kernel, the others to a portion kernel (the tcgen05 one for head sizes 64 and 128 with
+        pages it can load by TMA, else the mma.sync one).  Everything else (32-bit, other head sizes,
         `kernels="plain"`) goes to the plain kernel, which serves every case."""
         rt, ops = self.rt, self.rt.ops
         common = dict(q=q, cache=kv, out=out, block_tables=group.block_tables, num_heads=self.nh,
@@ -116,7 +117,10 @@ class GQAttention(Part):
         meta = dict(cu_q_lens=batch.cu_q_lens, ctx_lens=batch.ctx_lens, table_rows=batch.state_slots)
         n_dec = batch.decode_rows.numel()
         if batch.portion_rows.numel():
-            ops.attention_portions(rows=batch.portion_rows, max_q_len=batch.max_portion_len, **meta, **common)
+            tc = (hasattr(ops, "tc_attention_supports")
+                  and ops.tc_attention_supports(self.hd, q.dtype, self.nh, self.nkv, group.page_size))
+            portions = ops.attention_portions_tc if tc else ops.attention_portions
+            portions(rows=batch.portion_rows, max_q_len=batch.max_portion_len, **meta, **common)
         if n_dec:
             splits = self.decode_splits(n_dec, batch.max_decode_ctx)
             scratch = None

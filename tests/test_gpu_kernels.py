@@ -365,6 +365,47 @@ def test_attention_fast_mixed_batch(ops, nh, nkv, hd, page, window):
     assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
 
 
+TC_SHAPES = [(8, 2, 128, 16), (32, 8, 128, 16), (4, 4, 64, 8), (16, 2, 64, 32), (2, 1, 128, 128), (8, 8, 128, 64)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", TC_SHAPES)
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_tcgen05_portions(ops, nh, nkv, hd, page, window):
+    """The tcgen05 portion kernel: portions that start deep inside a context, end on and off page and tile
+    edges, a two-token portion, requests of very different length in one launch; unwritten cache rows hold NaN."""
+    ctx_lens = [37, 150, 333, 65, 700, 128, 257]
+    q_lens = [37, 9, 200, 2, 300, 128, 129]
+    assert ops.tc_attention_supports(hd, torch.bfloat16, nh, nkv, page)
+    case = _attention_case(nh, nkv, hd, page, ctx_lens, q_lens, window, torch.bfloat16, 33)
+    out = torch.full_like(case["q"], float("nan"))
+    ops.attention_portions_tc(q=case["q"], cache=case["cache"], out=out, rows=torch.arange(len(q_lens), dtype=torch.int32, device=DEV),
+                              cu_q_lens=case["cu_q_lens"], ctx_lens=case["ctx_lens"], table_rows=case["table_rows"],
+                              block_tables=case["block_tables"], num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                              page_size=page, window=window, scale=1 / math.sqrt(hd), max_q_len=max(q_lens))
+    assert ops.attention_tc_status(hd) == 0, "a bounded wait gave up"
+    assert torch.isfinite(out).all()
+    assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("where", ["far_back", "page_last", "page_first", "tile_last", "tile_first", "window_inside",
+                                   "window_outside"])
+def test_attention_tcgen05_finds_the_one_key_that_matters(ops, where):
+    nh, nkv, hd, page, ctx, window = 8, 2, 128, 16, 700, 0
+    key = {"far_back": 3, "page_last": 16 * 20 - 1, "page_first": 16 * 20, "tile_last": 128 * 3 - 1,
+           "tile_first": 128 * 3}.get(where)
+    if where.startswith("window"):
+        window = 100
+        key = ctx - 100 if where == "window_inside" else ctx - 101
+    case = _attention_case(nh, nkv, hd, page, [ctx], [40], window, torch.bfloat16, 34, spike=(0, key))
+    out = torch.full_like(case["q"], float("nan"))
+    ops.attention_portions_tc(q=case["q"], cache=case["cache"], out=out, rows=torch.zeros(1, dtype=torch.int32, device=DEV),
+                              cu_q_lens=case["cu_q_lens"], ctx_lens=case["ctx_lens"], table_rows=case["table_rows"],
+                              block_tables=case["block_tables"], num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                              page_size=page, window=window, scale=1 / math.sqrt(hd), max_q_len=40)
+    assert ops.attention_tc_status(hd) == 0
+    assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("splits", [1, 2, 7, 64])
 def test_attention_decode_any_number_of_splits(ops, splits):
     nh, nkv, hd, page = 8, 2, 128, 16

@@ -24,3 +24,11 @@ TINY_C = {
     "layer_types": ["full_attention", "sliding_attention", "full_attention"],
     "layer_order": [0, 1, 2, 1, [2, 2]],
 }
+
+# D: head size 64 with pages of 16, which the tcgen05 attention kernel serves
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 128,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 192,
+    "vocab_size": 600, "rope_theta": 300000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 640, "hidden_act": "silu",
+}
