@@ -36,6 +36,7 @@ MODEL_8B = {
 }
 CONTEXT = 4096          # benchmark context length
 CACHED = 2048           # tokens each request holds when decoding is timed
+PAGE_SIZE = 64          # tokens per cache page (--page-size)
 PREFILL_TOKENS = 2048
 
 
@@ -130,7 +131,7 @@ def breakdown(args) -> int:
     cfg = dict(MODEL_8B)
     cfg["num_hidden_layers"] = min(args.layers, 12)
     B, T = args.batch, PREFILL_TOKENS
-    ec = EngineConfig(dtype="bfloat16", page_size=16, max_cached_tokens=B * CONTEXT + T, max_num_seqs=B + 1,
+    ec = EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cached_tokens=B * CONTEXT + T, max_num_seqs=B + 1,
                       max_num_batched_tokens=T, max_model_len=CONTEXT, use_cuda_graphs=False)
     eng = Engine(config=cfg, random_seed=0, engine_config=ec)
     ops, blocks = eng.ops, eng.model.blocks
@@ -235,6 +236,7 @@ def breakdown(args) -> int:
 
 
 def main() -> int:
+    global PAGE_SIZE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -244,11 +246,13 @@ def main() -> int:
                     help="fewer layers than the model has (the record then names both numbers)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-graphs", action="store_true", help="do not capture decode steps in CUDA graphs")
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the end-to-end run")
     ap.add_argument("--breakdown", action="store_true",
                     help="instead of the bench line, print the time of every operation of a layer (decode at --batch "
                          "inside a CUDA graph, and a 2,048-token prefill), timed with CUDA events")
     args = ap.parse_args()
+    PAGE_SIZE = args.page_size
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:
@@ -268,7 +272,7 @@ def main() -> int:
     cfg = dict(MODEL_8B)
     cfg["num_hidden_layers"] = args.layers
     max_batch = 64 if not args.skip_points else args.batch
-    ec = EngineConfig(dtype="bfloat16", page_size=16, max_cached_tokens=max_batch * CONTEXT, max_num_seqs=max_batch,
+    ec = EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cached_tokens=max_batch * CONTEXT, max_num_seqs=max_batch,
                       max_num_batched_tokens=max(PREFILL_TOKENS, max_batch), prefill_chunk=PREFILL_TOKENS,
                       max_model_len=CONTEXT, use_cuda_graphs=not args.no_graphs)
     llm = LLM(config=cfg, random_seed=0, engine_config=ec)
@@ -376,7 +380,7 @@ def main() -> int:
         "config": {
             "model": "Qwen3-8B shape", "layers": args.layers, "layers_of_model": MODEL_8B["num_hidden_layers"],
             "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": I, "vocab": V,
-            "global_batch": args.batch, "seq_len": CONTEXT, "cached_tokens": CACHED, "page_size": 16,
+            "global_batch": args.batch, "seq_len": CONTEXT, "cached_tokens": CACHED, "page_size": PAGE_SIZE,
             "parallelism": "single GPU", "cuda_graphs": bool(getattr(eng, "graphs_enabled", False)),
             "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": pk["source"],
         },

@@ -71,11 +71,14 @@ class EngineConfig:
 
     The reference hard-codes these in its examples (page size 16 and 256 pages in
     examples/generate_paged.cpp:173-174, at most 4 requests in
-    include/minillm/runtime/continuous_batch_scheduler.h:43-45).
+    include/minillm/runtime/continuous_batch_scheduler.h:43-45).  Pages here hold 64 tokens by
+    default: a page of one head is then one 8 KB or 16 KB TMA box, and the tensor-core attention
+    over a prompt measured 104 us per layer against 164 us with pages of 16 (2,048 tokens, 32 query
+    and 8 key/value heads of 128); every power of two from 8 to 128 is served by the same kernels.
     """
 
     dtype: str = "bfloat16"              # "bfloat16" or "float32"
-    page_size: int = 16                  # tokens per cache page
+    page_size: int = 64                  # tokens per cache page
     max_cached_tokens: int = 0           # cache pool size in tokens; 0 = from free device memory
     gpu_memory_fraction: float = 0.85    # share of free memory the pool may take when sized automatically
     max_num_seqs: int = 64               # requests alive at once (also the number of state slots)

@@ -9,8 +9,8 @@
 //               each).  A page that holds keys beyond what the tile may see is copied by hand instead, with
 //               those rows zeroed, so that stale memory (NaN included) never reaches the tensor cores.
 //   warp 1      issues the matrix instructions: S = Q K^T (128 x 128 x HEAD_DIM) into one of two score
-//               buffers in tensor memory, and O_tile = P V (128 x HEAD_DIM x 128) into one of two output
-//               buffers; V is read as an MN-major operand, exactly as it lies in the cache.
+//               buffers in tensor memory, and O += P V (128 x HEAD_DIM x 128) into the output accumulator,
+//               also in tensor memory; V is read as an MN-major operand, exactly as it lies in the cache.
 //   warps 2..5  one row per thread: read S from tensor memory (tcgen05.ld), mask by absolute position, keep the
 //               running maximum and sum in 32-bit, write the probabilities as bfloat16 into the swizzled P
 //               tile, and fold each O_tile into the row's output accumulator, which lives in registers.
@@ -39,6 +39,10 @@ constexpr int HD = HEAD_DIM;
 constexpr int HALVES = HD / 64;        // 64-column (128-byte) halves of a row
 constexpr int BM = 128;                // rows per block
 constexpr int BN = 128;                // keys per tile
+#ifndef LLME_TC_BOX_ROWS
+#define LLME_TC_BOX_ROWS 64
+#endif
+constexpr int BOX_ROWS = LLME_TC_BOX_ROWS;   // most keys one TMA load brings; a tile's loads are started by as many lanes
 constexpr int THREADS = 192;
 constexpr int HALF_BYTES = 128 * 128;  // a [128 rows x 64 columns] bfloat16 tile with 128-byte rows
 constexpr int TILE_BYTES = HALVES * HALF_BYTES;
@@ -147,6 +151,23 @@ __device__ __forceinline__ void tmem_ld32(unsigned addr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_st32(unsigned addr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(addr),
+          "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -214,7 +235,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = bar->tmem_base;
     const unsigned tmem_s[2] = {tmem, tmem + 128};
-    const unsigned tmem_o[2] = {tmem + 256, tmem + 256 + 128};
+    const unsigned tmem_o = tmem + 256;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
@@ -223,11 +244,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(q_tile + h * HALF_BYTES, &map_q, h * 64, kvh * G, q0 + t_lo, &bar->q_full);
         }
-        const int rows_per_box = ps < BN ? ps : BN;            // rows one TMA load of the cache brings
+        const int rows_per_box = ps < BOX_ROWS ? ps : BOX_ROWS;   // rows one TMA load of the cache brings
         bool ok = true;
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int s = i & 1, round = i >> 1;
             const int j0 = (tile_first + i) * BN;
+            // the pages of this tile, looked up by the lanes side by side (one look-up per box, not one after
+            // the other in front of every copy)
+            int my_page = 0;
+            {
+                const int ja = j0 + lane * rows_per_box;
+                if (lane * rows_per_box < BN && ja + rows_per_box - 1 >= lo_min && ja <= hi_max) my_page = bt[ja / ps];
+            }
             for (int which = 0; which < 2 && ok; ++which) {       // keys, then values
                 unsigned long long* empty = which ? &bar->v_empty[s] : &bar->k_empty[s];
                 unsigned long long* full = which ? &bar->v_full[s] : &bar->k_full[s];
@@ -240,13 +268,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 unsigned tx = 0;
                 for (int b = 0; b < BN; b += rows_per_box) {
                     const int ja = j0 + b, jb = ja + rows_per_box - 1;
+                    const int page = __shfl_sync(0xffffffffu, my_page, b / rows_per_box);
                     if (jb < lo_min || ja > hi_max) continue;                 // nothing of it is needed
                     if (ja >= lo_min && jb <= hi_max) {
                         tx += (unsigned)(HALVES * rows_per_box * 128);
                         continue;
                     }
-                    const int blk = ja / ps;
-                    const long long row0 = (((long long)bt[blk] * 2 + which) * a.nkv + kvh) * ps + (ja - blk * ps);
+                    const long long row0 = (((long long)page * 2 + which) * a.nkv + kvh) * ps + (ja % ps);
                     for (int c = lane; c < rows_per_box * (HD / 8); c += 32) {
                         const int rr = c / (HD / 8), ch = c % (HD / 8);
                         const int j = ja + rr;
@@ -258,15 +286,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_expect_tx(full, tx);
-                    for (int b = 0; b < BN; b += rows_per_box) {
-                        const int ja = j0 + b, jb = ja + rows_per_box - 1;
-                        if (!(ja >= lo_min && jb <= hi_max)) continue;
-                        const int blk = ja / ps;
-                        const long long row0 = (((long long)bt[blk] * 2 + which) * a.nkv + kvh) * ps + (ja - blk * ps);
-                        for (int h = 0; h < HALVES; ++h)
-                            tma_load_2d(tile + h * HALF_BYTES + b * 128, &map_kv, h * 64, (int)row0, full);
+                if (lane == 0) mbar_expect_tx(full, tx);
+                __syncwarp();
+                // every lane starts the loads of its own box: issued from one thread, the many small boxes of
+                // small pages went out one after the other and took longer than the arithmetic on them
+                {
+                    const int box = lane / HALVES, h = lane % HALVES;
+                    const int b = box * rows_per_box;
+                    const int ja = j0 + b, jb = ja + rows_per_box - 1;
+                    const int page = __shfl_sync(0xffffffffu, my_page, box);
+                    if (b < BN && ja >= lo_min && jb <= hi_max) {
+                        const long long row0 = (((long long)page * 2 + which) * a.nkv + kvh) * ps + (ja % ps);
+                        tma_load_2d(tile + h * HALF_BYTES + b * 128, &map_kv, h * 64, (int)row0, full);
                     }
                 }
                 __syncwarp();
@@ -302,7 +333,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const int s = i & 1, round = i >> 1;
                 ok = ok && mbar_wait(&bar->p_full, i & 1, abort_flag, 23);
                 ok = ok && mbar_wait(&bar->v_full[s], round & 1, abort_flag, 24);
-                ok = ok && mbar_wait(&bar->o_empty[s], (round & 1) ^ 1, abort_flag, 25);
                 if (!ok) return;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned long long dv = desc_mn_major(v_tiles + s * TILE_BYTES);
@@ -310,11 +340,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     // P: 16 keys = 32 bytes further inside the 64-key half; V: 16 keys = two 1024-byte groups further
                     const unsigned long long dp = desc_k_major(p_tile + (kk >> 2) * HALF_BYTES) + 2 * (kk & 3);
-                    umma(tmem_o[s], dp, dv + (unsigned long long)(kk * (2048 >> 4)), id_o, kk > 0 ? 1u : 0u);
+                    umma(tmem_o, dp, dv + (unsigned long long)(kk * (2048 >> 4)), id_o, (i > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(&bar->v_empty[s]);
                 umma_commit(&bar->p_empty);
-                umma_commit(&bar->o_full[s]);
+                if (i == n_tiles - 1) umma_commit(&bar->o_full[0]);     // the output accumulator is complete
             };
             if (ok) issue_s(0);
             for (int i = 1; i < n_tiles && ok; ++i) {
@@ -324,7 +354,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (ok) issue_o(n_tiles - 1);
         }
     } else {
-        // ------------------------------------------------------------------ softmax, accumulation, output
+        // ------------------------------------------------------------------ softmax and output
+        // The output accumulator stays in tensor memory and is added to by the matrix warp tile after tile.
+        // A row's probabilities are taken relative to a reference maximum that is only moved when the true
+        // maximum has grown by more than RESCALE (in base-2 units): the final division by the sum, taken
+        // relative to the same reference, makes the result exact, and moving the reference means a round trip
+        // of the accumulator through registers, which then happens only in the first few tiles.
+        constexpr float RESCALE = 8.0f;
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;                 // this thread's row of the tile
         const int m = m0 + row;
@@ -334,10 +370,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int plo = a.window > 0 ? max(0, p - a.window + 1) : 0;
         const unsigned lane_off = (unsigned)(quarter * 32) << 16;
         const float sc = a.scale * LOG2E;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
-        float m_run = -INFINITY, l_run = 0.0f;
+        // what every row of this warp sees entirely, without a mask
+        const int warp_p_lo = start + min(q_len - 1, (m0 + quarter * 32) / G);
+        const int warp_p_hi = start + min(q_len - 1, (m0 + quarter * 32 + 31) / G);
+        const int warp_lo_last = a.window > 0 ? max(0, warp_p_hi - a.window + 1) : 0;
+        const bool warp_full = m0 + quarter * 32 + 31 < M;
+        float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int s = i & 1, round = i >> 1;
@@ -345,101 +383,97 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             ok = mbar_wait(&bar->s_full[s], round & 1, abort_flag, 30);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // pass 1: the row's maximum over the tile
-            float mx = -INFINITY;
-#pragma unroll 1
+            float sv[BN];
+#pragma unroll
             for (int c = 0; c < BN; c += 32) {
                 float v[32];
                 tmem_ld32(tmem_s[s] + lane_off + (unsigned)c, v);
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int j = j0 + c + e;
-                    if (j >= plo && j <= phi) mx = fmaxf(mx, v[e]);
+                for (int e = 0; e < 32; ++e) sv[c + e] = v[e];
+            }
+            // the scores are in registers: the buffer may be written again
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar->s_empty[s]);
+            const bool unmasked = warp_full && j0 + BN - 1 <= warp_p_lo && j0 >= warp_lo_last;
+            float mx = -INFINITY;
+            if (unmasked) {
+#pragma unroll
+                for (int e = 0; e < BN; ++e) mx = fmaxf(mx, sv[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < BN; ++e) {
+                    const int j = j0 + e;
+                    if (j < plo || j > phi) sv[e] = -INFINITY;
+                    mx = fmaxf(mx, sv[e]);
                 }
             }
-            const float m_new = fmaxf(m_run, mx * sc);
+            const float m_true = mx * sc;
+            const bool move = m_true > m_ref + RESCALE || (m_ref == -INFINITY && m_true > -INFINITY);
+            const float m_new = move ? m_true : m_ref;
             const float ref = m_new == -INFINITY ? 0.0f : m_new;
-            const float corr = fast_exp2(m_run - ref);
-            m_run = m_new;
-            // the P tile is free once P V of the tile before has read it
+            // the P tile is free, and the accumulator at rest, once P V of the tile before has finished
             ok = mbar_wait(&bar->p_empty, (i & 1) ^ 1, abort_flag, 31);
             if (!ok) break;
-            // pass 2: probabilities, their sum, and the bfloat16 P tile (row `row`, 16-byte chunk q at q ^ (row % 8))
-            float sum = 0.0f;
+            if (i > 0 && __any_sync(0xffffffffu, move)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float corr = move ? fast_exp2(m_ref - ref) : 1.0f;
+                l_run *= corr;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                float v[32];
-                tmem_ld32(tmem_s[s] + lane_off + (unsigned)c, v);
-                unsigned packed[16];
+                for (int c = 0; c < HD; c += 32) {
+                    float v[32];
+                    tmem_ld32(tmem_o + lane_off + (unsigned)c, v);
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int j = j0 + c + e;
-                    const float e0 = (j >= plo && j <= phi) ? fast_exp2(fmaf(v[e], sc, -ref)) : 0.0f;
-                    const float e1 = (j + 1 >= plo && j + 1 <= phi) ? fast_exp2(fmaf(v[e + 1], sc, -ref)) : 0.0f;
+                    for (int e = 0; e < 32; ++e) v[e] *= corr;
+                    tmem_st32(tmem_o + lane_off + (unsigned)c, v);
+                }
+            } else if (move) {
+                l_run *= fast_exp2(m_ref - ref);                 // first tile: nothing accumulated yet
+            }
+            m_ref = m_new;
+            // probabilities, their sum, and the bfloat16 P tile (row `row`, 16-byte chunk q at q ^ (row % 8))
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < BN; c += 8) {
+                unsigned pk[4];
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    const float e0 = fast_exp2(fmaf(sv[c + e], sc, -ref));        // a masked score is -inf: exactly 0
+                    const float e1 = fast_exp2(fmaf(sv[c + e + 1], sc, -ref));
                     sum += e0 + e1;
                     __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
-                    packed[e >> 1] = *reinterpret_cast<unsigned*>(&hh);
+                    pk[e >> 1] = *reinterpret_cast<unsigned*>(&hh);
                 }
-                unsigned char* half = p_tile + (c >> 6) * HALF_BYTES + row * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int q = ((c & 63) >> 3) + q4;          // chunk index within the 64-key half
-                    *reinterpret_cast<uint4*>(half + ((q ^ (row & 7)) << 4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
+                const int q = (c & 63) >> 3;                       // chunk index within the 64-key half
+                *reinterpret_cast<uint4*>(p_tile + (c >> 6) * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) =
+                    make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
-            l_run = l_run * corr + sum;
-            // S has been read and P written: tell the matrix warp
+            l_run += sum;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&bar->s_empty[s]);
-                mbar_arrive(&bar->p_full);
-            }
-            // fold the tile before into the accumulator (it is at the scale of the maximum before this tile),
-            // then bring the accumulator to the new scale
-            if (i > 0) {
-                const int sp = (i - 1) & 1;
-                ok = mbar_wait(&bar->o_full[sp], ((i - 1) >> 1) & 1, abort_flag, 32);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int c = 0; c < HD; c += 32) {
-                    float v[32];
-                    tmem_ld32(tmem_o[sp] + lane_off + (unsigned)c, v);
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) o[c + e] = (o[c + e] + v[e]) * corr;
-                }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar->o_empty[sp]);
-            }
+            if (lane == 0) mbar_arrive(&bar->p_full);
         }
+        if (ok) ok = mbar_wait(&bar->o_full[0], 0, abort_flag, 33);
         if (ok) {
-            const int sp = (n_tiles - 1) & 1;
-            ok = mbar_wait(&bar->o_full[sp], ((n_tiles - 1) >> 1) & 1, abort_flag, 33);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const float inv = 1.0f / l_run;
-                bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = 1.0f / l_run;
+            bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 32) {
+                float v[32];
+                tmem_ld32(tmem_o + lane_off + (unsigned)c, v);
+                if (row_ok) {
 #pragma unroll
-                for (int c = 0; c < HD; c += 32) {
-                    float v[32];
-                    tmem_ld32(tmem_o[sp] + lane_off + (unsigned)c, v);
-                    if (row_ok) {
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 pk;
+                        unsigned* pw = reinterpret_cast<unsigned*>(&pk);
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            uint4 pk;
-                            unsigned* pw = reinterpret_cast<unsigned*>(&pk);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const int d = c + q4 * 8 + 2 * e;
-                                __nv_bfloat162 hh = __floats2bfloat162_rn((o[d] + v[q4 * 8 + 2 * e]) * inv, (o[d + 1] + v[q4 * 8 + 2 * e + 1]) * inv);
-                                pw[e] = *reinterpret_cast<unsigned*>(&hh);
-                            }
-                            *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(v[q4 * 8 + 2 * e] * inv, v[q4 * 8 + 2 * e + 1] * inv);
+                            pw[e] = *reinterpret_cast<unsigned*>(&hh);
                         }
+                        *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
                     }
                 }
             }
@@ -508,7 +542,7 @@ LLME_API int llme_attention_tc(const void* q, long long q_tokens, long long tota
     {   // the cache as rows of HD columns; a box is one page (or 128 rows of a larger page) x 64 columns
         cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)total_cache_rows};
         cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-        cuuint32_t box[2] = {64, (cuuint32_t)(a.page_size < BN ? a.page_size : BN)};
+        cuuint32_t box[2] = {64, (cuuint32_t)(a.page_size < BOX_ROWS ? a.page_size : BOX_ROWS)};
         cuuint32_t es[2] = {1, 1};
         CUresult r = enc(&mkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(a.cache), dims, strides, box, es,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

@@ -25,18 +25,19 @@ import numpy as np
 
 
 def main(argv: Optional[List[str]] = None) -> int:
+    from ..config import EngineConfig
+
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (the cache pool is made for this many)")
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=EngineConfig().page_size)
     ap.add_argument("--max-requests", type=int, default=8, help="requests that may be live at once")
     ap.add_argument("--kernels", choices=["fast", "plain"], default="fast")
     args = ap.parse_args(argv)
 
-    from ..config import EngineConfig
     from .engine import Engine, StepEntry, StepError
 
     os.makedirs(args.out, exist_ok=True)

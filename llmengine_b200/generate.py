@@ -28,6 +28,8 @@ def parse_prompts(text: str) -> List[List[int]]:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
+    from .config import EngineConfig
+
     ap = argparse.ArgumentParser(prog="generate", description=__doc__.split("\n\n")[0])
     ap.add_argument("model", help="folder with config.json and model.safetensors")
     ap.add_argument("prompt", nargs="?", default="1", help="token ids, e.g. \"5,17,3\"; ';' separates prompts")
@@ -40,7 +42,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--top-p", type=float, default=0.0)
     ap.add_argument("--repetition-penalty", type=float, default=1.0)
     ap.add_argument("--seed", type=int, default=42)
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=EngineConfig().page_size)
     ap.add_argument("--max-cached-tokens", type=int, default=0, help="cache pool in tokens (0 = from free memory)")
     ap.add_argument("--max-num-seqs", type=int, default=64)
     ap.add_argument("--max-num-batched-tokens", type=int, default=2048)
