@@ -580,20 +580,40 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
         for (int s = lane; s < a.splits; s += 32) mm = fmaxf(mm, __ldcg(src + s * PART + HD));
         mm = warp_max(mm);
         const float ref = mm == -INFINITY ? 0.0f : mm;
+        // Splits are added in their own order, so the result does not depend on which block came last.  Lane s of
+        // a batch of 32 splits holds that split's weight; the partial outputs are fetched eight splits at a time
+        // (loads that do not wait for one another) and added with the weight passed from its lane.  An empty
+        // split holds zeros and has weight 0.
+        constexpr int KREGS = (HD + 31) / 32;
         float ll = 0.0f;
-        for (int s = lane; s < a.splits; s += 32) ll += exp2f(__ldcg(src + s * PART + HD) - ref) * __ldcg(src + s * PART + HD + 1);
-        ll = warp_sum(ll);
-        float acc[(HD + 31) / 32];
+        float acc[KREGS];
 #pragma unroll
-        for (int k = 0; k < (HD + 31) / 32; ++k) acc[k] = 0.0f;
-        for (int s = 0; s < a.splits; ++s) {                   // fixed order: the result does not depend on which block came last
-            const float w = exp2f(__ldcg(src + s * PART + HD) - ref);
+        for (int k = 0; k < KREGS; ++k) acc[k] = 0.0f;
+        for (int s0 = 0; s0 < a.splits; s0 += 32) {
+            float w_mine = 0.0f;
+            if (s0 + lane < a.splits) {
+                w_mine = exp2f(__ldcg(src + (s0 + lane) * PART + HD) - ref);
+                ll += w_mine * __ldcg(src + (s0 + lane) * PART + HD + 1);
+            }
+            const int n = min(32, a.splits - s0);
+            for (int j0 = 0; j0 < n; j0 += 8) {
+                float v[8][KREGS];
 #pragma unroll
-            for (int k = 0; k < (HD + 31) / 32; ++k) {
-                const int d = lane + 32 * k;
-                if (d < HD && w != 0.0f) acc[k] += w * __ldcg(src + s * PART + d);   // an empty split holds zeros and weight 0
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int k = 0; k < KREGS; ++k) {
+                        const int d = lane + 32 * k;
+                        v[j][k] = (j0 + j < n && d < HD) ? __ldcg(src + (size_t)(s0 + j0 + j) * PART + d) : 0.0f;
+                    }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float w = __shfl_sync(0xffffffffu, w_mine, (j0 + j) & 31);
+#pragma unroll
+                    for (int k = 0; k < KREGS; ++k) acc[k] += w * v[j][k];
+                }
             }
         }
+        ll = warp_sum(ll);
         bf16* dst = a.out + ((size_t)t * a.nh + head) * HD;
         const float inv = 1.0f / ll;
 #pragma unroll

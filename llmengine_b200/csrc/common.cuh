@@ -52,11 +52,17 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <stdlib.h>
+#include <string.h>
 #include <utility>
 inline bool llme_pdl_enabled() {
     static const bool on = [] {
-        const char* e = getenv("LLME_PDL");
-        return e && e[0] == '1';
+        const char* e = getenv("LLME_PDL");   // "1": every kernel; else a list of source files, e.g. "gemm_skinny.cu,elementwise.cu"
+        if (!e) return false;
+        if (e[0] == '1') return true;
+        const char* base = __BASE_FILE__;
+        for (const char* p = base; *p; ++p)
+            if (*p == '/') base = p + 1;
+        return strstr(e, base) != nullptr;
     }();
     return on;
 }

@@ -306,8 +306,7 @@ class CudaOps:
         assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
         if M == 0:
             return out
-        if (M <= 16 and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        if self.skinny_supports(x, w, out):
             # a handful of tokens: this package's weight-streaming kernel
             lib = self._lib("gemm_skinny")
             rc = lib.llme_gemm_skinny_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w.data_ptr()),
@@ -323,6 +322,26 @@ class CudaOps:
             torch.mm(x, w.t(), out=out)
         else:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+        return out
+
+    def skinny_supports(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+        """Whether the weight-streaming kernel for a handful of tokens takes this product."""
+        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= 16 and x.shape[1] % 8 == 0
+                and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1 and x.stride(0) % 8 == 0
+                and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def linear_swiglu(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out[M, I] = silu(x @ Wg^T) * (x @ Wu^T) with w_gate_up = [Wg | Wu] stacked by rows, in one kernel;
+        only where skinny_supports() holds."""
+        lib = self._lib("gemm_skinny")
+        M, K = x.shape
+        inter = out.shape[1]
+        assert w_gate_up.shape == (2 * inter, K) and out.shape[0] == M and self.skinny_supports(x, w_gate_up, out)
+        rc = lib.llme_gemm_skinny_swiglu_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w_gate_up.data_ptr()),
+                                              c_longlong(w_gate_up.stride(0)), c_void_p(out.data_ptr()),
+                                              c_int(_code(out.dtype)), c_longlong(out.stride(0)), c_int(M), c_int(inter),
+                                              c_int(K), self._stream())
+        self._check(lib, rc, "gemm_skinny_swiglu")
         return out
 
     def linear_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

@@ -33,9 +33,13 @@ class SwiGLU(Part):
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
         rt, ops = self.rt, self.rt.ops
         T = h.shape[0]
-        gate_up = rt.buffer("gate_up", T, 2 * self.inter, rt.dtype)
-        ops.linear(h, self.w_gate_up, gate_up)
         act = rt.buffer("act", T, self.inter, rt.dtype)
-        ops.swiglu(gate_up, act)
+        fused = getattr(ops, "skinny_supports", None)
+        if fused is not None and fused(h, self.w_gate_up, act):
+            ops.linear_swiglu(h, self.w_gate_up, act)         # a handful of tokens: product and activation in one kernel
+        else:
+            gate_up = rt.buffer("gate_up", T, 2 * self.inter, rt.dtype)
+            ops.linear(h, self.w_gate_up, gate_up)
+            ops.swiglu(gate_up, act)
         delta = rt.buffer("ffn_out", T, self.hidden, torch.float32)
         return ops.linear(act, self.w_down, delta)

@@ -188,6 +188,30 @@ def test_skinny_gemm_rows_do_not_depend_on_the_batch(ops):
         assert torch.equal(part, full[:m])
 
 
+@pytest.mark.parametrize("M,inter,K", [(8, 12288, 4096), (1, 3072, 1024), (16, 100, 72), (3, 8, 8), (11, 5000, 264), (7, 20, 520)])
+def test_skinny_gemm_with_swiglu(ops, M, inter, K):
+    """Product and activation in one kernel against the product followed by the activation kernel (the same
+    arithmetic, so the same bits) and against 64-bit arithmetic."""
+    a = _rand(M, K, dtype=torch.bfloat16, seed=46)
+    w = _rand(2 * inter, K, dtype=torch.bfloat16, seed=47, scale=0.08)
+    fused = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(a, w, fused)
+    gate_up = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device=DEV)
+    ops.linear(a, w, gate_up)
+    two = torch.empty(M, inter, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu(gate_up, two)
+    assert torch.equal(fused, two)
+    y = a.double() @ w.double().t()
+    g, u = y[:, :inter], y[:, inter:]
+    want = (g / (1 + torch.exp(-g)) * u).cpu()
+    got = fused.double().cpu()
+    assert torch.isfinite(got).all()
+    # gate and up pass through bfloat16 (a relative 2^-9 each; |d silu / d gate| <= 1.1), and so may the result
+    tol = 2e-5 * math.sqrt(K) * float(want.abs().max() + 1)
+    bound = (1.1 * (g.abs() * u.abs()).cpu() + 2 * want.abs()) * 2 ** -8 + tol
+    assert ((got - want).abs() <= bound).all()
+
+
 # ----------------------------------------------------------------------------- QK norm + rope + cache write
 def _paged_layout(T, page_size, num_pages, seed):
     """Scatter T consecutive positions over pages in a scrambled order."""
