@@ -176,7 +176,6 @@ def breakdown(args) -> int:
         q = torch.empty(rows, qs, device="cuda", dtype=torch.bfloat16)
         ao = torch.empty(rows, qs, device="cuda", dtype=torch.bfloat16)
         mo = torch.empty(rows, H, device="cuda")
-        gu = torch.empty(rows, 2 * I, device="cuda", dtype=torch.bfloat16)
         act = torch.empty(rows, I, device="cuda", dtype=torch.bfloat16)
         grp = batch.groups[0]
 
@@ -194,8 +193,7 @@ def breakdown(args) -> int:
             ("attention", lambda l: blocks[l].mixer.attend(q, eng._caches[l].kv, ao, batch, grp), 0),
             ("output product", lambda l: ops.linear(ao, blocks[l].mixer.w_o, mo), H * qs),
             ("rmsnorm + residual add (feed-forward)", lambda l: blocks[l].ffn_norm.forward(x, delta=mo), 0),
-            ("gate|up product", lambda l: ops.linear(h, blocks[l].ffn.w_gate_up, gu), 2 * I * H),
-            ("swiglu", lambda l: ops.swiglu(gu, act), 0),
+            ("gate|up product + swiglu", lambda l: ops.linear_swiglu(h, blocks[l].ffn.w_gate_up, act), 2 * I * H),
             ("down product", lambda l: ops.linear(act, blocks[l].ffn.w_down, mo), H * I),
         ]
         out, total = [], 0.0

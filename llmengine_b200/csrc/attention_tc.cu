@@ -11,9 +11,12 @@
 //   warp 1      issues the matrix instructions: S = Q K^T (128 x 128 x HEAD_DIM) into one of two score
 //               buffers in tensor memory, and O += P V (128 x HEAD_DIM x 128) into the output accumulator,
 //               also in tensor memory; V is read as an MN-major operand, exactly as it lies in the cache.
-//   warps 2..5  one row per thread: read S from tensor memory (tcgen05.ld), mask by absolute position, keep the
-//               running maximum and sum in 32-bit, write the probabilities as bfloat16 into the swizzled P
-//               tile, and fold each O_tile into the row's output accumulator, which lives in registers.
+//   warps 2..9  softmax: two threads per row, 64 keys of the tile each (a warp may only touch the 32 lanes of
+//               tensor memory given by its index modulo 4, so warps w and w+4 share the same 32 rows and
+//               split the columns).  They read S from tensor memory (tcgen05.ld), mask by absolute
+//               position, agree on the row's maximum through shared memory, keep the running reference
+//               maximum and their half of the sum in 32-bit, and write the probabilities as bfloat16 into
+//               the swizzled P tile.  The output accumulator stays in tensor memory.
 //
 // The score of tile i+1 is computed while the softmax of tile i runs, and P V of tile i while the softmax of
 // tile i+1 runs.  Every mbarrier wait is bounded; a wait that gives up sets an error flag (read with
@@ -40,10 +43,10 @@ constexpr int HALVES = HD / 64;        // 64-column (128-byte) halves of a row
 constexpr int BM = 128;                // rows per block
 constexpr int BN = 128;                // keys per tile
 #ifndef LLME_TC_BOX_ROWS
-#define LLME_TC_BOX_ROWS 64
+#define LLME_TC_BOX_ROWS 32
 #endif
 constexpr int BOX_ROWS = LLME_TC_BOX_ROWS;   // most keys one TMA load brings; a tile's loads are started by as many lanes
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;           // producer, matrix warp, eight softmax warps
 constexpr int HALF_BYTES = 128 * 128;  // a [128 rows x 64 columns] bfloat16 tile with 128-byte rows
 constexpr int TILE_BYTES = HALVES * HALF_BYTES;
 constexpr unsigned WAIT_LIMIT = 1u << 20;
@@ -174,11 +177,27 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Diagnostic build (-DLLME_TC_TRACE): the first block writes the time of its pipeline events, tile by tile.
+#ifdef LLME_TC_TRACE
+__device__ unsigned long long g_trace[16][64];
+__device__ __forceinline__ void trace(int what, int i) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 64) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_trace[what][i] = t;
+    }
+}
+#else
+__device__ __forceinline__ void trace(int, int) {}
+#endif
+
 struct Barriers {
     unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
     unsigned long long s_full[2], s_empty[2], p_full, p_empty, o_full[2], o_empty[2];
     unsigned tmem_base;
     int abort_flag;
+    float row_max[2][2][BM];      // [tile parity][column half][row]: the halves' maxima of a tile
+    float row_sum[2][BM];         // [column half][row]: the halves' sums at the end
 };
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -215,10 +234,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bar->k_full[s], 1); mbar_init(&bar->k_empty[s], 1);
             mbar_init(&bar->v_full[s], 1); mbar_init(&bar->v_empty[s], 1);
-            mbar_init(&bar->s_full[s], 1); mbar_init(&bar->s_empty[s], 4);
-            mbar_init(&bar->o_full[s], 1); mbar_init(&bar->o_empty[s], 4);
+            mbar_init(&bar->s_full[s], 1); mbar_init(&bar->s_empty[s], 8);
+            mbar_init(&bar->o_full[s], 1); mbar_init(&bar->o_empty[s], 8);
         }
-        mbar_init(&bar->p_full, 4);
+        mbar_init(&bar->p_full, 8);
         mbar_init(&bar->p_empty, 1);
         bar->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -244,62 +263,73 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(q_tile + h * HALF_BYTES, &map_q, h * 64, kvh * G, q0 + t_lo, &bar->q_full);
         }
-        const int rows_per_box = ps < BOX_ROWS ? ps : BOX_ROWS;   // rows one TMA load of the cache brings
+        // Rows one TMA load of the cache brings: a power of two (pages of 8..64 tokens, or 64 rows of a larger
+        // page).  A lane looks after one TMA load of a tile (box lane / HALVES, 64-column half lane % HALVES): it looks up the box's page (one tile ahead of its use, so
+        // that the look-up's latency is not in front of every tile's copies), and decides whether the box is
+        // needed whole (a TMA load), in part (copied by hand), or not at all.  No division in the loop: the
+        // producer's instructions are a dependent chain, and at 1 block per SM nothing hides their latency.
+        const int rows_per_box = ps < BOX_ROWS ? ps : BOX_ROWS;
+        const int box_shift = __ffs(rows_per_box) - 1;
+        const int n_boxes = BN >> box_shift;
+        const int ps_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
+        constexpr int H_SHIFT = HALVES == 2 ? 1 : 0;
+        const unsigned load_bytes = (unsigned)(rows_per_box * 128);     // one TMA load: a box of one 64-column half
+        const int my_box = lane >> H_SHIFT, my_half = lane & (HALVES - 1);
+        const long long head_rows = (long long)kvh * ps;                 // row of this head within a page's K (or V) block
+        const long long page_rows = (long long)2 * a.nkv * ps, v_rows = (long long)a.nkv * ps;
         bool ok = true;
+        auto first_row = [&](int i) -> long long {                       // cache row of this lane's box in tile i (its K rows), or -1
+            const int ja = (tile_first + i) * BN + (my_box << box_shift);
+            if (i >= n_tiles || my_box >= n_boxes || ja + rows_per_box - 1 < lo_min || ja > hi_max) return -1;
+            const int blk = ps_shift >= 0 ? ja >> ps_shift : ja / ps;
+            return (long long)bt[blk] * page_rows + head_rows + (ja - blk * ps);
+        };
+        long long next_row = first_row(0);
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int s = i & 1, round = i >> 1;
             const int j0 = (tile_first + i) * BN;
-            // the pages of this tile, looked up by the lanes side by side (one look-up per box, not one after
-            // the other in front of every copy)
-            int my_page = 0;
-            {
-                const int ja = j0 + lane * rows_per_box;
-                if (lane * rows_per_box < BN && ja + rows_per_box - 1 >= lo_min && ja <= hi_max) my_page = bt[ja / ps];
-            }
+            const long long my_row = next_row;
+            next_row = first_row(i + 1);
+            const int ja = j0 + (my_box << box_shift), jb = ja + rows_per_box - 1;
+            const bool whole = my_row >= 0 && ja >= lo_min && jb <= hi_max;
+            const unsigned whole_mask = __ballot_sync(0xffffffffu, whole);                 // one bit per TMA load
+            const unsigned part_mask = __ballot_sync(0xffffffffu, my_row >= 0 && !whole && my_half == 0);
+            const unsigned tx = (unsigned)__popc(whole_mask) * load_bytes;
             for (int which = 0; which < 2 && ok; ++which) {       // keys, then values
                 unsigned long long* empty = which ? &bar->v_empty[s] : &bar->k_empty[s];
                 unsigned long long* full = which ? &bar->v_full[s] : &bar->k_full[s];
                 unsigned char* tile = (which ? v_tiles : k_tiles) + s * TILE_BYTES;
                 ok = mbar_wait(empty, (round & 1) ^ 1, abort_flag, 10 + which) && !*abort_flag;
                 if (!ok) break;
+                if (lane == 0) trace(8 + which, i);
                 // First the boxes that straddle an edge of the visible range: they are copied by hand, visible
                 // rows only, the rest zeroed.  Then, after those writes are published, one lane arms the barrier
-                // and starts the TMA loads of the boxes that are needed whole.
-                unsigned tx = 0;
-                for (int b = 0; b < BN; b += rows_per_box) {
-                    const int ja = j0 + b, jb = ja + rows_per_box - 1;
-                    const int page = __shfl_sync(0xffffffffu, my_page, b / rows_per_box);
-                    if (jb < lo_min || ja > hi_max) continue;                 // nothing of it is needed
-                    if (ja >= lo_min && jb <= hi_max) {
-                        tx += (unsigned)(HALVES * rows_per_box * 128);
-                        continue;
+                // and the lanes start the TMA loads of the boxes that are needed whole.
+                if (part_mask) {
+                    for (unsigned rest = part_mask; rest; rest &= rest - 1) {
+                        const int src_lane = __ffs(rest) - 1, b = (src_lane >> H_SHIFT) << box_shift;
+                        const long long row0 = __shfl_sync(0xffffffffu, my_row, src_lane) + (which ? v_rows : 0);
+                        for (int c = lane; c < rows_per_box * (HD / 8); c += 32) {
+                            const int rr = c / (HD / 8), ch = c % (HD / 8);
+                            const int j = j0 + b + rr;
+                            uint4 v = make_uint4(0, 0, 0, 0);
+                            if (j >= lo_min && j <= hi_max) v = *reinterpret_cast<const uint4*>(a.cache + (row0 + rr) * HD + ch * 8);
+                            const int h = ch >> 3, q = ch & 7, row = b + rr;
+                            *reinterpret_cast<uint4*>(tile + h * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) = v;
+                        }
                     }
-                    const long long row0 = (((long long)page * 2 + which) * a.nkv + kvh) * ps + (ja % ps);
-                    for (int c = lane; c < rows_per_box * (HD / 8); c += 32) {
-                        const int rr = c / (HD / 8), ch = c % (HD / 8);
-                        const int j = ja + rr;
-                        uint4 v = make_uint4(0, 0, 0, 0);
-                        if (j >= lo_min && j <= hi_max) v = *reinterpret_cast<const uint4*>(a.cache + (row0 + rr) * HD + ch * 8);
-                        const int h = ch >> 3, q = ch & 7, row = b + rr;
-                        *reinterpret_cast<uint4*>(tile + h * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) = v;
-                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_expect_tx(full, tx);
                 __syncwarp();
+                if (lane == 0) trace(10 + which, i);
                 // every lane starts the loads of its own box: issued from one thread, the many small boxes of
                 // small pages went out one after the other and took longer than the arithmetic on them
-                {
-                    const int box = lane / HALVES, h = lane % HALVES;
-                    const int b = box * rows_per_box;
-                    const int ja = j0 + b, jb = ja + rows_per_box - 1;
-                    const int page = __shfl_sync(0xffffffffu, my_page, box);
-                    if (b < BN && ja >= lo_min && jb <= hi_max) {
-                        const long long row0 = (((long long)page * 2 + which) * a.nkv + kvh) * ps + (ja % ps);
-                        tma_load_2d(tile + h * HALF_BYTES + b * 128, &map_kv, h * 64, (int)row0, full);
-                    }
-                }
+                if (whole)
+                    tma_load_2d(tile + my_half * HALF_BYTES + (my_box << box_shift) * 128, &map_kv, my_half * 64,
+                                (int)(my_row + (which ? v_rows : 0)), full);
+                if (lane == 0) trace(which, i);
                 __syncwarp();
             }
         }
@@ -328,6 +358,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 umma_commit(&bar->k_empty[s]);
                 umma_commit(&bar->s_full[s]);
+                trace(2, i);
             };
             auto issue_o = [&](int i) {
                 const int s = i & 1, round = i >> 1;
@@ -345,6 +376,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 umma_commit(&bar->v_empty[s]);
                 umma_commit(&bar->p_empty);
                 if (i == n_tiles - 1) umma_commit(&bar->o_full[0]);     // the output accumulator is complete
+                trace(3, i);
             };
             if (ok) issue_s(0);
             for (int i = 1; i < n_tiles && ok; ++i) {
@@ -361,7 +393,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // relative to the same reference, makes the result exact, and moving the reference means a round trip
         // of the accumulator through registers, which then happens only in the first few tiles.
         constexpr float RESCALE = 8.0f;
-        const int quarter = warp & 3;
+        constexpr int BH = BN / 2;                           // keys of a tile per thread
+        constexpr int OC = HD / 2;                           // columns of the output accumulator per thread
+        const int quarter = warp & 3;                        // the 32 lanes of tensor memory this warp may touch
+        const int ch = (warp - 2) >> 2;                      // which half of the columns it takes
         const int row = quarter * 32 + lane;                 // this thread's row of the tile
         const int m = m0 + row;
         const bool row_ok = m < M;
@@ -375,66 +410,79 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int warp_p_hi = start + min(q_len - 1, (m0 + quarter * 32 + 31) / G);
         const int warp_lo_last = a.window > 0 ? max(0, warp_p_hi - a.window + 1) : 0;
         const bool warp_full = m0 + quarter * 32 + 31 < M;
+        // the two warps of a quarter meet at a named barrier of their own (64 threads)
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
-        for (int i = 0; i < n_tiles && ok; ++i) {
+        for (int i = 0; i < n_tiles; ++i) {
             const int s = i & 1, round = i >> 1;
-            const int j0 = (tile_first + i) * BN;
-            ok = mbar_wait(&bar->s_full[s], round & 1, abort_flag, 30);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float sv[BN];
-#pragma unroll
-            for (int c = 0; c < BN; c += 32) {
-                float v[32];
-                tmem_ld32(tmem_s[s] + lane_off + (unsigned)c, v);
-#pragma unroll
-                for (int e = 0; e < 32; ++e) sv[c + e] = v[e];
-            }
-            // the scores are in registers: the buffer may be written again
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->s_empty[s]);
-            const bool unmasked = warp_full && j0 + BN - 1 <= warp_p_lo && j0 >= warp_lo_last;
+            const int j0 = (tile_first + i) * BN + ch * BH;      // first key of this thread's half
+            ok = ok && mbar_wait(&bar->s_full[s], round & 1, abort_flag, 30);
+            float sv[BH];
             float mx = -INFINITY;
-            if (unmasked) {
+            if (warp == 2 && lane == 0) trace(4, i);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int e = 0; e < BN; ++e) mx = fmaxf(mx, sv[e]);
-            } else {
+                for (int c = 0; c < BH; c += 32) {
+                    float v[32];
+                    tmem_ld32(tmem_s[s] + lane_off + (unsigned)(ch * BH + c), v);
 #pragma unroll
-                for (int e = 0; e < BN; ++e) {
-                    const int j = j0 + e;
-                    if (j < plo || j > phi) sv[e] = -INFINITY;
-                    mx = fmaxf(mx, sv[e]);
+                    for (int e = 0; e < 32; ++e) sv[c + e] = v[e];
+                }
+                // the scores are in registers: the buffer may be written again
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar->s_empty[s]);
+                const bool unmasked = warp_full && j0 + BH - 1 <= warp_p_lo && j0 >= warp_lo_last;
+                if (unmasked) {
+#pragma unroll
+                    for (int e = 0; e < BH; ++e) mx = fmaxf(mx, sv[e]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < BH; ++e) {
+                        const int j = j0 + e;
+                        if (j < plo || j > phi) sv[e] = -INFINITY;
+                        mx = fmaxf(mx, sv[e]);
+                    }
                 }
             }
+            // the row's maximum over both halves (a warp that gave up still comes to the barrier: its partner waits there)
+            bar->row_max[s][ch][row] = mx;
+            pair_sync();
+            if (!ok || *abort_flag) { ok = false; continue; }
+            if (warp == 2 && lane == 0) trace(5, i);
+            mx = fmaxf(mx, bar->row_max[s][ch ^ 1][row]);
             const float m_true = mx * sc;
             const bool move = m_true > m_ref + RESCALE || (m_ref == -INFINITY && m_true > -INFINITY);
             const float m_new = move ? m_true : m_ref;
             const float ref = m_new == -INFINITY ? 0.0f : m_new;
             // the P tile is free, and the accumulator at rest, once P V of the tile before has finished
             ok = mbar_wait(&bar->p_empty, (i & 1) ^ 1, abort_flag, 31);
-            if (!ok) break;
+            if (!ok) continue;
+            if (warp == 2 && lane == 0) trace(6, i);
             if (i > 0 && __any_sync(0xffffffffu, move)) {
+                // both warps of the quarter see the same maxima and take the same decision; each rescales its
+                // half of the accumulator's columns
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float corr = move ? fast_exp2(m_ref - ref) : 1.0f;
                 l_run *= corr;
 #pragma unroll 1
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = 0; c < OC; c += 32) {
                     float v[32];
-                    tmem_ld32(tmem_o + lane_off + (unsigned)c, v);
+                    tmem_ld32(tmem_o + lane_off + (unsigned)(ch * OC + c), v);
 #pragma unroll
                     for (int e = 0; e < 32; ++e) v[e] *= corr;
-                    tmem_st32(tmem_o + lane_off + (unsigned)c, v);
+                    tmem_st32(tmem_o + lane_off + (unsigned)(ch * OC + c), v);
                 }
             } else if (move) {
                 l_run *= fast_exp2(m_ref - ref);                 // first tile: nothing accumulated yet
             }
             m_ref = m_new;
-            // probabilities, their sum, and the bfloat16 P tile (row `row`, 16-byte chunk q at q ^ (row % 8))
+            // probabilities, their sum, and this half of the bfloat16 P tile (row `row`, 16-byte chunk q at q ^ (row % 8))
             float sum = 0.0f;
 #pragma unroll
-            for (int c = 0; c < BN; c += 8) {
+            for (int c = 0; c < BH; c += 8) {
                 unsigned pk[4];
 #pragma unroll
                 for (int e = 0; e < 8; e += 2) {
@@ -444,8 +492,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
                     pk[e >> 1] = *reinterpret_cast<unsigned*>(&hh);
                 }
-                const int q = (c & 63) >> 3;                       // chunk index within the 64-key half
-                *reinterpret_cast<uint4*>(p_tile + (c >> 6) * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) =
+                const int q = c >> 3;                              // chunk index within the 64-key half
+                *reinterpret_cast<uint4*>(p_tile + ch * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) =
                     make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
             l_run += sum;
@@ -453,16 +501,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar->p_full);
+            if (warp == 2 && lane == 0) trace(7, i);
         }
+        // the row's sum over both halves
+        bar->row_sum[ch][row] = l_run;
+        pair_sync();
+        l_run += bar->row_sum[ch ^ 1][row];
         if (ok) ok = mbar_wait(&bar->o_full[0], 0, abort_flag, 33);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l_run;
-            bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD;
+            bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD + ch * OC;
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
+            for (int c = 0; c < OC; c += 32) {
                 float v[32];
-                tmem_ld32(tmem_o + lane_off + (unsigned)c, v);
+                tmem_ld32(tmem_o + lane_off + (unsigned)(ch * OC + c), v);
                 if (row_ok) {
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
@@ -506,6 +559,12 @@ static_assert(SMEM_BYTES <= 232448, "the block's shared memory must fit an SM");
 }  // namespace
 
 LLME_API int llme_attention_tc_head_dim() { return HD; }
+
+#ifdef LLME_TC_TRACE
+LLME_API int llme_attention_tc_trace(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 16 * 64);
+}
+#endif
 
 // Whether this kernel takes the problem: a page size that divides 128 and is at least 8 (a TMA box of whole
 // pages with whole swizzle groups), and a group size (query heads per key/value head) that divides 128.

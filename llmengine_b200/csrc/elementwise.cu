@@ -336,110 +336,175 @@ template <> struct Vec2<__nv_bfloat16> {
     static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 v) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y); }
 };
 
-template <typename I, typename O, typename G, int NP>
+// TPW: tokens per warp.  With many tokens a warp takes the same head of TPW consecutive tokens and issues all
+// their loads (head, gains, cos/sin rows) before the first reduction, so that four times as many bytes are in
+// flight per warp; with few tokens (a decode step) every (token, head) pair gets a warp of its own.
+template <typename I, typename O, typename G, int NP, int TPW>
 __global__ void qkv_post_vec_kernel(QkvArgs a) {
     pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     pdl_wait();                // everything below reads or writes what earlier kernels touch
-    const int warps_per_block = blockDim.x >> 5;
+    // grid: x = group of TPW tokens, y = group of heads (one per warp of the block); no division per warp
     const int lane = threadIdx.x & 31;
-    const long long wid = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int heads = a.nh + 2 * a.nkv;
-    if (wid >= (long long)a.tokens * heads) return;
-    const int t = (int)(wid / heads);
-    const int h = (int)(wid % heads);
+    const int t0 = (int)blockIdx.x * TPW;
+    const int h = (int)blockIdx.y * (int)(blockDim.x >> 5) + (int)(threadIdx.x >> 5);
+    if (h >= heads) return;
     const int hd = a.hd, half = hd >> 1;
+    const int page_shift = (a.page_size & (a.page_size - 1)) == 0 ? __ffs(a.page_size) - 1 : -1;
 
     if (h >= a.nh + a.nkv) {                       // value head: copy into the cache
         if (!a.cache || !a.v_in) return;
-        const int slot = a.slot_mapping[t];
-        if (slot < 0) return;
         const int kvh = h - a.nh - a.nkv;
-        const I* src = (const I*)a.v_in + (size_t)t * a.v_stride + (size_t)kvh * hd;
-        const int page = slot / a.page_size, off = slot % a.page_size;
-        O* dst = (O*)a.cache + ((((size_t)page * 2 + 1) * a.nkv + kvh) * a.page_size + off) * hd;
+        float2 v[TPW][2 * NP];
+        int slot[TPW];
 #pragma unroll
-        for (int i = 0; i < 2 * NP; ++i) {
-            const int d = 2 * (lane + 32 * i);
-            if (d < hd) Vec2<O>::store(dst + d, Vec2<I>::load(src + d));
+        for (int u = 0; u < TPW; ++u) {
+            const int t = t0 + u;
+            slot[u] = t < a.tokens ? a.slot_mapping[t] : -1;
+            const I* src = (const I*)a.v_in + (size_t)(t < a.tokens ? t : t0) * a.v_stride + (size_t)kvh * hd;
+#pragma unroll
+            for (int i = 0; i < 2 * NP; ++i) {
+                const int d = 2 * (lane + 32 * i);
+                if (d < hd) v[u][i] = Vec2<I>::load(src + d);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < TPW; ++u) {
+            if (slot[u] < 0) continue;
+            const int page = page_shift >= 0 ? slot[u] >> page_shift : slot[u] / a.page_size;
+            const int off = slot[u] - page * a.page_size;
+            O* dst = (O*)a.cache + ((((size_t)page * 2 + 1) * a.nkv + kvh) * a.page_size + off) * hd;
+#pragma unroll
+            for (int i = 0; i < 2 * NP; ++i) {
+                const int d = 2 * (lane + 32 * i);
+                if (d < hd) Vec2<O>::store(dst + d, v[u][i]);
+            }
         }
         return;
     }
 
     const bool is_q = h < a.nh;
     const int head = is_q ? h : h - a.nh;
-    const I* src;
-    if (is_q) {
-        if (!a.q_in) return;
-        src = (const I*)a.q_in + (size_t)t * a.q_stride + (size_t)head * hd;
-    } else {
-        if (!a.k_in) return;
-        src = (const I*)a.k_in + (size_t)t * a.k_stride + (size_t)head * hd;
-    }
+    const I* base = (const I*)(is_q ? a.q_in : a.k_in);
+    if (!base) return;
+    const long long stride = is_q ? a.q_stride : a.k_stride;
     const G* gain = (const G*)(is_q ? a.q_gain : a.k_gain);
 
-    float2 lo[NP], hi[NP];
-    float ss = 0.0f;
+    // every load first: the heads, the gains, the rows of the cos/sin table and the cache slots
+    float2 lo[TPW][NP], hi[TPW][NP], co[TPW][NP], si[TPW][NP], g0[NP], g1[NP];
+    int slot[TPW];
 #pragma unroll
-    for (int i = 0; i < NP; ++i) {
-        const int d = 2 * (lane + 32 * i);
-        if (d < half) {
-            lo[i] = Vec2<I>::load(src + d);
-            hi[i] = Vec2<I>::load(src + d + half);
-            ss += lo[i].x * lo[i].x + lo[i].y * lo[i].y + hi[i].x * hi[i].x + hi[i].y * hi[i].y;
+    for (int u = 0; u < TPW; ++u) {
+        const int t = t0 + u < a.tokens ? t0 + u : t0;
+        const I* src = base + (size_t)t * stride + (size_t)head * hd;
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const int d = 2 * (lane + 32 * i);
+            if (d < half) {
+                lo[u][i] = Vec2<I>::load(src + d);
+                hi[u][i] = Vec2<I>::load(src + d + half);
+            }
+        }
+        slot[u] = (!is_q && a.cache && t0 + u < a.tokens) ? a.slot_mapping[t] : -1;
+        if (a.cos_sin) {
+            int pos = a.positions[t];
+            pos = pos < 0 ? 0 : (pos >= a.max_positions ? a.max_positions - 1 : pos);   // the host refuses such positions
+            const float* cs = a.cos_sin + (size_t)pos * hd;
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                const int d = 2 * (lane + 32 * i);
+                if (d < half) {
+                    co[u][i] = *reinterpret_cast<const float2*>(cs + d);
+                    si[u][i] = *reinterpret_cast<const float2*>(cs + half + d);
+                }
+            }
         }
     }
     if (gain) {
-        ss = warp_sum(ss);
-        const float rinv = 1.0f / sqrtf(ss / (float)hd + a.eps);
 #pragma unroll
         for (int i = 0; i < NP; ++i) {
             const int d = 2 * (lane + 32 * i);
             if (d < half) {
-                const float2 g0 = Vec2<G>::load(gain + d), g1 = Vec2<G>::load(gain + d + half);
-                lo[i].x = (lo[i].x * rinv) * g0.x; lo[i].y = (lo[i].y * rinv) * g0.y;
-                hi[i].x = (hi[i].x * rinv) * g1.x; hi[i].y = (hi[i].y * rinv) * g1.y;
+                g0[i] = Vec2<G>::load(gain + d);
+                g1[i] = Vec2<G>::load(gain + d + half);
             }
         }
     }
-    if (a.cos_sin) {
-        int pos = a.positions[t];
-        pos = pos < 0 ? 0 : (pos >= a.max_positions ? a.max_positions - 1 : pos);   // the host refuses such positions
-        const float* cs = a.cos_sin + (size_t)pos * hd;
+
 #pragma unroll
-        for (int i = 0; i < NP; ++i) {
-            const int d = 2 * (lane + 32 * i);
-            if (d < half) {
-                const float2 c = *reinterpret_cast<const float2*>(cs + d);
-                const float2 s = *reinterpret_cast<const float2*>(cs + half + d);
-                const float2 x0 = lo[i], x1 = hi[i];
-                lo[i] = make_float2(x0.x * c.x - x1.x * s.x, x0.y * c.y - x1.y * s.y);
-                hi[i] = make_float2(x0.x * s.x + x1.x * c.x, x0.y * s.y + x1.y * c.y);
+    for (int u = 0; u < TPW; ++u) {
+        if (t0 + u >= a.tokens) break;
+        const int t = t0 + u;
+        if (gain) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                const int d = 2 * (lane + 32 * i);
+                if (d < half) ss += lo[u][i].x * lo[u][i].x + lo[u][i].y * lo[u][i].y + hi[u][i].x * hi[u][i].x + hi[u][i].y * hi[u][i].y;
+            }
+            ss = warp_sum(ss);
+            const float rinv = 1.0f / sqrtf(ss / (float)hd + a.eps);
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                const int d = 2 * (lane + 32 * i);
+                if (d < half) {
+                    lo[u][i].x = (lo[u][i].x * rinv) * g0[i].x; lo[u][i].y = (lo[u][i].y * rinv) * g0[i].y;
+                    hi[u][i].x = (hi[u][i].x * rinv) * g1[i].x; hi[u][i].y = (hi[u][i].y * rinv) * g1[i].y;
+                }
             }
         }
-    }
-    O* q_dst = (is_q && a.q_out) ? (O*)a.q_out + ((size_t)t * a.nh + head) * hd : nullptr;
-    O* k_dst = (!is_q && a.k_out) ? (O*)a.k_out + ((size_t)t * a.nkv + head) * hd : nullptr;
-    O* c_dst = nullptr;
-    if (!is_q && a.cache) {
-        const int slot = a.slot_mapping[t];
-        if (slot >= 0) {
-            const int page = slot / a.page_size, off = slot % a.page_size;
+        if (a.cos_sin) {
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                const int d = 2 * (lane + 32 * i);
+                if (d < half) {
+                    const float2 c = co[u][i], sn = si[u][i];
+                    const float2 x0 = lo[u][i], x1 = hi[u][i];
+                    lo[u][i] = make_float2(x0.x * c.x - x1.x * sn.x, x0.y * c.y - x1.y * sn.y);
+                    hi[u][i] = make_float2(x0.x * sn.x + x1.x * c.x, x0.y * sn.y + x1.y * c.y);
+                }
+            }
+        }
+        O* q_dst = (is_q && a.q_out) ? (O*)a.q_out + ((size_t)t * a.nh + head) * hd : nullptr;
+        O* k_dst = (!is_q && a.k_out) ? (O*)a.k_out + ((size_t)t * a.nkv + head) * hd : nullptr;
+        O* c_dst = nullptr;
+        if (slot[u] >= 0) {
+            const int page = page_shift >= 0 ? slot[u] >> page_shift : slot[u] / a.page_size;
+            const int off = slot[u] - page * a.page_size;
             c_dst = (O*)a.cache + ((((size_t)page * 2 + 0) * a.nkv + head) * a.page_size + off) * hd;
         }
-    }
 #pragma unroll
-    for (int i = 0; i < NP; ++i) {
-        const int d = 2 * (lane + 32 * i);
-        if (d < half) {
-            if (q_dst) { Vec2<O>::store(q_dst + d, lo[i]); Vec2<O>::store(q_dst + d + half, hi[i]); }
-            if (k_dst) { Vec2<O>::store(k_dst + d, lo[i]); Vec2<O>::store(k_dst + d + half, hi[i]); }
-            if (c_dst) { Vec2<O>::store(c_dst + d, lo[i]); Vec2<O>::store(c_dst + d + half, hi[i]); }
+        for (int i = 0; i < NP; ++i) {
+            const int d = 2 * (lane + 32 * i);
+            if (d < half) {
+                if (q_dst) { Vec2<O>::store(q_dst + d, lo[u][i]); Vec2<O>::store(q_dst + d + half, hi[u][i]); }
+                if (k_dst) { Vec2<O>::store(k_dst + d, lo[u][i]); Vec2<O>::store(k_dst + d + half, hi[u][i]); }
+                if (c_dst) { Vec2<O>::store(c_dst + d, lo[u][i]); Vec2<O>::store(c_dst + d + half, hi[u][i]); }
+            }
         }
     }
 }
 
+constexpr int QKV_WARPS_PER_BLOCK = 8;
+constexpr int QKV_TOKENS_PER_WARP = 4;
+
+template <typename I, typename O, typename G, int NP>
+static bool launch_qkv_vec_np(const QkvArgs& a, cudaStream_t s) {
+    const int heads = a.nh + 2 * a.nkv;
+    const unsigned head_groups = (unsigned)((heads + QKV_WARPS_PER_BLOCK - 1) / QKV_WARPS_PER_BLOCK);
+    if (head_groups > 65535u) return false;
+    // enough (token, head) pairs to fill the GPU several times over: a warp takes four tokens
+    if ((long long)a.tokens * heads >= 148LL * 64 * QKV_TOKENS_PER_WARP) {
+        const unsigned token_groups = (unsigned)((a.tokens + QKV_TOKENS_PER_WARP - 1) / QKV_TOKENS_PER_WARP);
+        llme_launch(qkv_post_vec_kernel<I, O, G, NP, QKV_TOKENS_PER_WARP>, dim3(token_groups, head_groups), dim3(QKV_WARPS_PER_BLOCK * 32), 0, s, a);
+    } else {
+        llme_launch(qkv_post_vec_kernel<I, O, G, NP, 1>, dim3((unsigned)a.tokens, head_groups), dim3(QKV_WARPS_PER_BLOCK * 32), 0, s, a);
+    }
+    return true;
+}
+
 template <typename I, typename O, typename G>
-static bool launch_qkv_vec(const QkvArgs& a, unsigned blocks, int threads, cudaStream_t s) {
+static bool launch_qkv_vec(const QkvArgs& a, cudaStream_t s) {
     if (a.hd % 4 || a.hd > 512) return false;
     if ((a.q_stride | a.k_stride | a.v_stride) & 1) return false;
     const uintptr_t ptrs = (uintptr_t)a.q_in | (uintptr_t)a.k_in | (uintptr_t)a.v_in | (uintptr_t)a.q_gain |
@@ -447,10 +512,9 @@ static bool launch_qkv_vec(const QkvArgs& a, unsigned blocks, int threads, cudaS
                            (uintptr_t)a.cache;
     if (ptrs % 8) return false;
     const int half = a.hd / 2;
-    if (half <= 64) llme_launch(qkv_post_vec_kernel<I, O, G, 1>, dim3(blocks), dim3(threads), 0, s, a);
-    else if (half <= 128) llme_launch(qkv_post_vec_kernel<I, O, G, 2>, dim3(blocks), dim3(threads), 0, s, a);
-    else llme_launch(qkv_post_vec_kernel<I, O, G, 4>, dim3(blocks), dim3(threads), 0, s, a);
-    return true;
+    if (half <= 64) return launch_qkv_vec_np<I, O, G, 1>(a, s);
+    if (half <= 128) return launch_qkv_vec_np<I, O, G, 2>(a, s);
+    return launch_qkv_vec_np<I, O, G, 4>(a, s);
 }
 
 template <typename I, typename O>
@@ -460,9 +524,9 @@ static int dispatch_qkv_gain(const QkvArgs& a, cudaStream_t s) {
     const long long blocks = (warps + wpb - 1) / wpb;
     if (blocks > 2147483647LL) LLME_REFUSE("qkv_post: too many (token, head) pairs for one launch");
     if (a.gain_dtype == LLME_F32 || !(a.q_gain || a.k_gain)) {
-        if (launch_qkv_vec<I, O, float>(a, (unsigned)blocks, wpb * 32, s)) LLME_LAUNCH_STATUS();
+        if (launch_qkv_vec<I, O, float>(a, s)) LLME_LAUNCH_STATUS();
     } else if (a.gain_dtype == LLME_BF16) {
-        if (launch_qkv_vec<I, O, __nv_bfloat16>(a, (unsigned)blocks, wpb * 32, s)) LLME_LAUNCH_STATUS();
+        if (launch_qkv_vec<I, O, __nv_bfloat16>(a, s)) LLME_LAUNCH_STATUS();
     }
     if (a.gain_dtype == LLME_F32) llme_launch(qkv_post_kernel<I, O, float>, dim3((unsigned)blocks), dim3(wpb * 32), 0, s, a);
     else if (a.gain_dtype == LLME_BF16) llme_launch(qkv_post_kernel<I, O, __nv_bfloat16>, dim3((unsigned)blocks), dim3(wpb * 32), 0, s, a);

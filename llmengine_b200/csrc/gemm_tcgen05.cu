@@ -112,6 +112,7 @@ struct TcArgs {
     void* out; long long ldo;
     int M, N, K;
     int m_tiles, n_tiles;
+    int inter;      // ACT kernels: W = [gate | up] with `inter` rows each, out[M, inter] = silu(gate) * up
 };
 
 __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
@@ -127,7 +128,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
 // epilogue warps read tile i out of one buffer, the MMA warp already fills the other with tile i+1.
 // TMA_STORE: the epilogue stages 32-row x 128-byte pieces in (swizzled) shared memory and writes them with
 // cp.async.bulk.tensor stores; otherwise it stores from registers (any alignment of the output).
-template <int BN, int STAGES, typename O, bool TMA_STORE>
+// ACT: the SwiGLU of a feed-forward in the epilogue.  W = [gate | up]; a tile's BN accumulator columns are
+// BN/2 gate rows and the BN/2 up rows of the same outputs (two TMA boxes per stage), and the epilogue
+// stores silu(gate) * up, BN/2 columns per tile, both factors rounded to bfloat16 first as they are when
+// the activation is a kernel of its own.
+template <int BN, int STAGES, typename O, bool TMA_STORE, bool ACT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_o, TcArgs a) {
@@ -178,14 +183,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             unsigned it = 0, first_in_flight = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                const int m0 = (t % a.m_tiles) * BM, n0 = (t / a.m_tiles) * BN;
+                const int m0 = (t % a.m_tiles) * BM, n0 = (t / a.m_tiles) * (ACT ? BN / 2 : BN);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const unsigned s = it % STAGES;
                     ok = mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, 1) && !*abort_flag;
                     if (!ok) break;
                     mbar_expect_tx(full + s, A_BYTES + B_BYTES);
                     tma_load_2d(a_tiles + s * A_BYTES, &map_x, kb * BK, m0, full + s);
-                    tma_load_2d(b_tiles + s * B_BYTES, &map_w, kb * BK, n0, full + s);
+                    if (ACT) {
+                        // gate rows n0.., then the up rows of the same outputs (a box of map_w has BN/2 rows)
+                        tma_load_2d(b_tiles + s * B_BYTES, &map_w, kb * BK, n0, full + s);
+                        tma_load_2d(b_tiles + s * B_BYTES + B_BYTES / 2, &map_w, kb * BK, a.inter + n0, full + s);
+                    } else {
+                        tma_load_2d(b_tiles + s * B_BYTES, &map_w, kb * BK, n0, full + s);
+                    }
                 }
             }
             if (!ok) {
@@ -233,7 +244,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         int i = 0, piece = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++i) {
-            const int m0 = (t % a.m_tiles) * BM, n0 = (t / a.m_tiles) * BN;
+            constexpr int OUT_COLS = ACT ? BN / 2 : BN;        // output columns of a tile
+            const int m0 = (t % a.m_tiles) * BM, n0 = (t / a.m_tiles) * OUT_COLS;
+            const int n_limit = ACT ? a.inter : a.N;
             const int b = i & 1;
             ok = mbar_wait(acc_full + b, (i >> 1) & 1, abort_flag, 3);
             if (!ok) break;
@@ -241,7 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const int row = m0 + quarter * 32 + lane;
             const unsigned tmem_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(b * BN);
 #pragma unroll 1
-            for (int c = 0; c < BN; c += COLS) {
+            for (int c = 0; c < OUT_COLS; c += COLS) {
                 unsigned char* buf = my_staging + (piece & 1) * 4096;
                 if (TMA_STORE) {
                     // the store that last used this buffer (two pieces ago) must have read it
@@ -252,8 +265,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 for (int half = 0; half < COLS / 32; ++half) {
                     unsigned v[32];
                     tmem_ld_32x32(tmem_row + (unsigned)(c + half * 32), v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + COLS >= BN && half == COLS / 32 - 1) {
+                    if (ACT) {
+                        unsigned up[32];
+                        tmem_ld_32x32(tmem_row + (unsigned)(BN / 2 + c + half * 32), up);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j])));
+                            const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j])));
+                            v[j] = __float_as_uint((g / (1.0f + expf(-g))) * u);
+                        }
+                    } else {
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    }
+                    if (c + COLS >= OUT_COLS && half == COLS / 32 - 1) {
                         // the tile has left tensor memory: hand the buffer back to the MMA warp
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         __syncwarp();
@@ -281,11 +306,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         }
                     } else {
                         const int col = n0 + c + half * 32;
-                        if (row < a.M && col < a.N) {
+                        if (row < a.M && col < n_limit) {
                             O* dst = reinterpret_cast<O*>(a.out) + (size_t)row * a.ldo + col;
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (col + j < a.N) dst[j] = from_f32<O>(__uint_as_float(v[j]));
+                                if (col + j < n_limit) dst[j] = from_f32<O>(__uint_as_float(v[j]));
                         }
                     }
                 }
@@ -294,7 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     __syncwarp();
                     if (lane == 0) {
                         // rows or columns of the piece that lie outside the matrix are clipped by the TMA
-                        if (m0 + quarter * 32 < a.M && n0 + c < a.N) tma_store_2d(&map_o, buf, n0 + c, m0 + quarter * 32);
+                        if (m0 + quarter * 32 < a.M && n0 + c < n_limit) tma_store_2d(&map_o, buf, n0 + c, m0 + quarter * 32);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                     ++piece;
@@ -351,19 +376,19 @@ int sm_count() {
     return n;
 }
 
-template <int BN, int STAGES, typename O, bool TMA_STORE>
+template <int BN, int STAGES, typename O, bool TMA_STORE, bool ACT>
 int launch_kernel(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const TcArgs& a, cudaStream_t s) {
     constexpr size_t smem = 1024 + (size_t)STAGES * (BM + BN) * BK * 2 + (TMA_STORE ? 4 * 2 * 4096 : 0) + (2 * STAGES + 4) * 8 + 16;
     static_assert(smem <= 232448, "the block's shared memory must fit an SM");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, O, TMA_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, O, TMA_STORE, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LLME_REFUSE("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
     const int tiles = a.m_tiles * a.n_tiles;
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    gemm_tc_kernel<BN, STAGES, O, TMA_STORE><<<grid, THREADS, smem, s>>>(mx, mw, mo, a);
+    gemm_tc_kernel<BN, STAGES, O, TMA_STORE, ACT><<<grid, THREADS, smem, s>>>(mx, mw, mo, a);
     LLME_LAUNCH_STATUS();
 }
 
@@ -379,10 +404,23 @@ int launch(const void* x, long long ldx, const void* w, long long ldw, TcArgs a,
     if (tma_store) {
         const CUtensorMapDataType t = sizeof(O) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
         if (int rc = make_map(&mo, a.out, t, (int)sizeof(O), a.M, a.N, a.ldo, 32, 128 / (int)sizeof(O))) return rc;
-        return launch_kernel<BN, STAGES, O, true>(mx, mw, mo, a, s);
+        return launch_kernel<BN, STAGES, O, true, false>(mx, mw, mo, a, s);
     }
     mo = mx;
-    return launch_kernel<BN, STAGES, O, false>(mx, mw, mo, a, s);
+    return launch_kernel<BN, STAGES, O, false, false>(mx, mw, mo, a, s);
+}
+
+// out[M, inter] = silu(x Wg^T) * (x Wu^T), W = [Wg | Wu]: tiles of BN/2 outputs, boxes of BN/2 rows of W.
+template <int BN, int STAGES, typename O>
+int launch_act(const void* x, long long ldx, const void* w, long long ldw, TcArgs a, cudaStream_t s) {
+    alignas(64) CUtensorMap mx, mw, mo;
+    if (int rc = make_map(&mx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.M, a.K, ldx, BM, BK)) return rc;
+    if (int rc = make_map(&mw, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.N, a.K, ldw, BN / 2, BK)) return rc;
+    a.m_tiles = (a.M + BM - 1) / BM;
+    a.n_tiles = (a.inter + BN / 2 - 1) / (BN / 2);
+    const CUtensorMapDataType t = sizeof(O) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    if (int rc = make_map(&mo, a.out, t, (int)sizeof(O), a.M, a.inter, a.ldo, 32, 128 / (int)sizeof(O))) return rc;
+    return launch_kernel<BN, STAGES, O, true, true>(mx, mw, mo, a, s);
 }
 
 }  // namespace
@@ -400,10 +438,26 @@ LLME_API int llme_gemm_tc_bf16(const void* x, long long ldx, const void* w, long
     if (!x || !w || !out) LLME_REFUSE("gemm_tc: null pointer");
     if (!llme_gemm_tc_supports(M, N, K, ldx, ldw, ldo)) LLME_REFUSE("gemm_tc: M=%d N=%d K=%d ldx=%lld ldw=%lld ldo=%lld is not supported (K and operand strides must be multiples of 8)", M, N, K, ldx, ldw, ldo);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_tc: operands must be 16-byte aligned");
-    TcArgs a{out, ldo, M, N, K, 0, 0};
+    TcArgs a{out, ldo, M, N, K, 0, 0, 0};
     if (out_dtype == LLME_F32) return N > 128 ? launch<256, 4, float>(x, ldx, w, ldw, a, stream) : launch<128, 6, float>(x, ldx, w, ldw, a, stream);
     if (out_dtype == LLME_BF16) return N > 128 ? launch<256, 4, bf16>(x, ldx, w, ldw, a, stream) : launch<128, 6, bf16>(x, ldx, w, ldw, a, stream);
     LLME_REFUSE("gemm_tc: unsupported output dtype %d", out_dtype);
+}
+
+// 1 if llme_gemm_tc_swiglu_bf16 takes this problem (the output is written with TMA stores: 16-byte aligned rows).
+LLME_API int llme_gemm_tc_swiglu_supports(int M, int inter, int K, long long ldx, long long ldw, long long ldo) {
+    return M >= 1 && inter >= 8 && inter <= (1 << 29) && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldo >= inter && ldo % 8 == 0;
+}
+
+// out[M, inter] (bfloat16) = silu(x Wg^T) * (x Wu^T) with W = [Wg | Wu] stacked by rows ([2 * inter, K]).
+LLME_API int llme_gemm_tc_swiglu_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo,
+                                      int M, int inter, int K, cudaStream_t stream) {
+    if (M <= 0 || inter <= 0) return 0;
+    if (!x || !w || !out) LLME_REFUSE("gemm_tc: null pointer");
+    if (!llme_gemm_tc_swiglu_supports(M, inter, K, ldx, ldw, ldo)) LLME_REFUSE("gemm_tc: M=%d inter=%d K=%d ldx=%lld ldw=%lld ldo=%lld is not supported (K and strides must be multiples of 8)", M, inter, K, ldx, ldw, ldo);
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16) LLME_REFUSE("gemm_tc: operands and output must be 16-byte aligned");
+    TcArgs a{out, ldo, M, 2 * inter, K, 0, 0, inter};
+    return launch_act<256, 4, bf16>(x, ldx, w, ldw, a, stream);
 }
 
 // Reads and clears the error flag of the kernels (synchronises the device).  0 = no wait ever gave up.

@@ -330,18 +330,37 @@ class CudaOps:
                 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
+    def _tc_swiglu_supports(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+        return (self.use_tcgen05 and x.dtype == w.dtype == out.dtype == torch.bfloat16 and x.shape[0] >= 128
+                and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and out.shape[1] >= 8
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+    def linear_swiglu_supports(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
+        """Whether linear_swiglu() takes this product: a handful of tokens (the weight-streaming kernel) or at
+        least 128 of them (the tcgen05 kernel), bfloat16."""
+        return self.skinny_supports(x, w_gate_up, out) or self._tc_swiglu_supports(x, w_gate_up, out)
+
     def linear_swiglu(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out[M, I] = silu(x @ Wg^T) * (x @ Wu^T) with w_gate_up = [Wg | Wu] stacked by rows, in one kernel;
-        only where skinny_supports() holds."""
-        lib = self._lib("gemm_skinny")
+        only where linear_swiglu_supports() holds."""
         M, K = x.shape
         inter = out.shape[1]
-        assert w_gate_up.shape == (2 * inter, K) and out.shape[0] == M and self.skinny_supports(x, w_gate_up, out)
-        rc = lib.llme_gemm_skinny_swiglu_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w_gate_up.data_ptr()),
-                                              c_longlong(w_gate_up.stride(0)), c_void_p(out.data_ptr()),
-                                              c_int(_code(out.dtype)), c_longlong(out.stride(0)), c_int(M), c_int(inter),
-                                              c_int(K), self._stream())
-        self._check(lib, rc, "gemm_skinny_swiglu")
+        assert w_gate_up.shape == (2 * inter, K) and out.shape[0] == M
+        if self.skinny_supports(x, w_gate_up, out):
+            lib = self._lib("gemm_skinny")
+            rc = lib.llme_gemm_skinny_swiglu_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w_gate_up.data_ptr()),
+                                                  c_longlong(w_gate_up.stride(0)), c_void_p(out.data_ptr()),
+                                                  c_int(_code(out.dtype)), c_longlong(out.stride(0)), c_int(M), c_int(inter),
+                                                  c_int(K), self._stream())
+            self._check(lib, rc, "gemm_skinny_swiglu")
+            return out
+        assert self._tc_swiglu_supports(x, w_gate_up, out)
+        lib = self._lib("gemm_tcgen05")
+        rc = lib.llme_gemm_tc_swiglu_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w_gate_up.data_ptr()),
+                                          c_longlong(w_gate_up.stride(0)), c_void_p(out.data_ptr()), c_longlong(out.stride(0)),
+                                          c_int(M), c_int(inter), c_int(K), self._stream())
+        self._check(lib, rc, "gemm_tcgen05_swiglu")
         return out
 
     def linear_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

@@ -34,9 +34,9 @@ class SwiGLU(Part):
         rt, ops = self.rt, self.rt.ops
         T = h.shape[0]
         act = rt.buffer("act", T, self.inter, rt.dtype)
-        fused = getattr(ops, "skinny_supports", None)
+        fused = getattr(ops, "linear_swiglu_supports", None)
         if fused is not None and fused(h, self.w_gate_up, act):
-            ops.linear_swiglu(h, self.w_gate_up, act)         # a handful of tokens: product and activation in one kernel
+            ops.linear_swiglu(h, self.w_gate_up, act)         # product and activation in one kernel
         else:
             gate_up = rt.buffer("gate_up", T, 2 * self.inter, rt.dtype)
             ops.linear(h, self.w_gate_up, gate_up)

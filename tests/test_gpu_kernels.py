@@ -212,6 +212,31 @@ def test_skinny_gemm_with_swiglu(ops, M, inter, K):
     assert ((got - want).abs() <= bound).all()
 
 
+@pytest.mark.parametrize("M,inter,K", [(2048, 12288, 4096), (128, 128, 64), (300, 1000, 264), (129, 72, 520), (1000, 136, 8)])
+def test_tcgen05_gemm_with_swiglu(ops, M, inter, K):
+    """The tcgen05 product with the activation in its epilogue against the product followed by the activation
+    kernel, and against 64-bit arithmetic; widths that end inside a tile."""
+    a = _rand(M, K, dtype=torch.bfloat16, seed=48)
+    w = _rand(2 * inter, K, dtype=torch.bfloat16, seed=49, scale=0.08)
+    fused = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.linear_swiglu_supports(a, w, fused)
+    ops.linear_swiglu(a, w, fused)
+    assert ops.linear_tc_status() == 0
+    gate_up = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device=DEV)
+    ops.linear_tc(a, w, gate_up)
+    two = torch.empty(M, inter, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu(gate_up, two)
+    assert torch.equal(fused, two)
+    y = a.double() @ w.double().t()
+    g, u = y[:, :inter], y[:, inter:]
+    want = (g / (1 + torch.exp(-g)) * u).cpu()
+    got = fused.double().cpu()
+    assert torch.isfinite(got).all()
+    tol = 2e-5 * math.sqrt(K) * float(want.abs().max() + 1)
+    bound = (1.1 * (g.abs() * u.abs()).cpu() + 2 * want.abs()) * 2 ** -8 + tol
+    assert ((got - want).abs() <= bound).all()
+
+
 # ----------------------------------------------------------------------------- QK norm + rope + cache write
 def _paged_layout(T, page_size, num_pages, seed):
     """Scatter T consecutive positions over pages in a scrambled order."""
