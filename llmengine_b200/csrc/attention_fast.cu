@@ -368,13 +368,16 @@ constexpr int PART = HD + 2;
 constexpr int COUNTER_WORDS = 65536;
 __device__ __forceinline__ float* partials(const FastAttnArgs& a) { return a.scratch + COUNTER_WORDS; }
 constexpr int SUB = 16;           // keys per sub-tile
+constexpr int PAGE_TAB = 512;     // block-table entries a block keeps in shared memory (longer ranges are read from global memory)
 constexpr int DSTAGES = 3;        // stage buffers per warp (two sub-tiles in flight while one is used); two blocks fit an SM
 constexpr int STAGE_ELEMS = 2 * SUB * LDS;   // K rows then V rows
 
 // One warp loads keys [j0, j0+16) (K and V) into its stage buffer; keys outside [lo, hi] become zeros.
 // When the page size is a multiple of 16 (page_shift >= 4) the 16 keys lie in one page: one look-up in the
 // block table, and every lane's addresses differ from one another only by constants.
-__device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, const int* bt, int kvh, int nkv, int ps,
+// `bt` points at the entry of block `bt_first` (the request's row of the block table in global memory, or the
+// part of it that the block has copied into shared memory).
+__device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, const int* bt, int bt_first, int kvh, int nkv, int ps,
                                               int page_shift, int j0, int lo, int hi) {
     const int lane = threadIdx.x & 31;
     constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per key row
@@ -383,7 +386,7 @@ __device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, cons
         const int blk = j0 >> page_shift;
         const bool any = j0 + SUB - 1 >= lo && j0 <= hi;
         const bf16* kbase = cache;
-        if (any) kbase = cache + ((((size_t)bt[blk] * 2) * nkv + kvh) * ps + (j0 - (blk << page_shift))) * HD;
+        if (any) kbase = cache + ((((size_t)bt[blk - bt_first] * 2) * nkv + kvh) * ps + (j0 - (blk << page_shift))) * HD;
         const size_t v_off = (size_t)nkv * ps * HD;
 #pragma unroll
         for (int c = lane; c < TOTAL; c += 32) {
@@ -403,7 +406,7 @@ __device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, cons
         const bf16* ksrc = cache;
         if (valid) {
             const int blk = page_shift >= 0 ? (j >> page_shift) : (j / ps);
-            const int page = bt[blk];
+            const int page = bt[blk - bt_first];
             ksrc = cache + ((((size_t)page * 2) * nkv + kvh) * ps + (j - blk * ps)) * HD + ch * 8;
         }
         cp_async_16(dst + r * LDS + ch * 8, ksrc, valid);
@@ -446,6 +449,21 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
 
+    // The block's part of the block table goes to shared memory first, all entries at once: looked up in
+    // global memory one by one, in front of every sub-tile's copies, each entry cost a warp a memory
+    // round trip (8 of them per warp at 2,048 cached tokens, about a third of the kernel's time).
+    __shared__ int page_tab[PAGE_TAB];
+    const int* tab = bt;
+    int tab_first = 0;
+    if (my_first <= my_last) {
+        const int blk_first = (max(my_first * SUB, lo)) / ps, blk_last = min(my_last * SUB + SUB - 1, p) / ps;
+        if (blk_last - blk_first < PAGE_TAB) {
+            for (int i = threadIdx.x; i <= blk_last - blk_first; i += THREADS) page_tab[i] = bt[blk_first + i];
+            tab = page_tab;
+            tab_first = blk_first;
+            __syncthreads();
+        }
+    }
     if (my_first <= my_last) {
         // the query rows, loaded by the whole block
         {
@@ -464,7 +482,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
 #pragma unroll
         for (int st = 0; st < DSTAGES - 1; ++st) {
             const int sub = my_first + warp + 4 * st;
-            if (sub <= my_last) load_sub_tile(mine + st * STAGE_ELEMS, a.cache, bt, kvh, a.nkv, ps, page_shift, sub * SUB, lo, p);
+            if (sub <= my_last) load_sub_tile(mine + st * STAGE_ELEMS, a.cache, tab, tab_first, kvh, a.nkv, ps, page_shift, sub * SUB, lo, p);
             cp_async_commit();
         }
         cp_async_wait<DSTAGES - 1>();                       // the query rows have landed
@@ -482,7 +500,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
         for (int sub = my_first + warp; sub <= my_last; sub += 4, ++n) {
             const int ahead = sub + 4 * (DSTAGES - 1);
             if (ahead <= my_last)
-                load_sub_tile(mine + ((n + DSTAGES - 1) % DSTAGES) * STAGE_ELEMS, a.cache, bt, kvh, a.nkv, ps, page_shift,
+                load_sub_tile(mine + ((n + DSTAGES - 1) % DSTAGES) * STAGE_ELEMS, a.cache, tab, tab_first, kvh, a.nkv, ps, page_shift,
                               ahead * SUB, lo, p);
             cp_async_commit();
             cp_async_wait<DSTAGES - 1>();                   // this lane's copies of sub-tile n are done

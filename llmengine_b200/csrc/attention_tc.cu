@@ -213,12 +213,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = a.rows[blockIdx.z];
-    const int kvh = blockIdx.y;
+    // blockIdx.x = tile * nkv + head: the blocks with the most keys, of all heads, start first
+    const int kvh = (int)(blockIdx.x % (unsigned)a.nkv), tile_index = (int)(blockIdx.x / (unsigned)a.nkv);
     const int G = a.nh / a.nkv;
     const int q0 = a.cu_q_lens[r];
     const int q_len = a.cu_q_lens[r + 1] - q0;
     const int M = q_len * G;
-    const int m0 = ((M + BM - 1) / BM - 1 - (int)blockIdx.x) * BM;     // the tiles with the most keys start first
+    const int m0 = ((M + BM - 1) / BM - 1 - tile_index) * BM;
     if (m0 < 0) return;
     const int start = a.ctx_lens[r] - q_len;
     const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
@@ -583,7 +584,7 @@ LLME_API int llme_attention_tc(const void* q, long long q_tokens, long long tota
     if (!q || !a.out || !a.cache || !a.rows || !a.cu_q_lens || !a.ctx_lens || !a.table_rows || !a.block_tables)
         LLME_REFUSE("attention_tc: null pointer");
     if (!llme_attention_tc_supports(a.nh, a.nkv, a.page_size)) LLME_REFUSE("attention_tc: %d/%d heads with pages of %d are not supported", a.nh, a.nkv, a.page_size);
-    if (a.n_rows > 65535 || a.nkv > 65535) LLME_REFUSE("attention_tc: grid too large");
+    if (a.n_rows > 65535) LLME_REFUSE("attention_tc: grid too large");
     EncodeTiledFn enc = encode_fn();
     if (!enc) LLME_REFUSE("attention_tc: cuTensorMapEncodeTiled is not available in this driver");
     const int G = a.nh / a.nkv;
@@ -615,8 +616,8 @@ LLME_API int llme_attention_tc(const void* q, long long q_tokens, long long tota
         configured = true;
     }
     const long long tiles = ((long long)max_q_len * G + BM - 1) / BM;
-    if (tiles > 2147483647LL) LLME_REFUSE("attention_tc: grid too large");
-    dim3 grid((unsigned)tiles, a.nkv, a.n_rows);
+    if (tiles * a.nkv > 2147483647LL) LLME_REFUSE("attention_tc: grid too large");
+    dim3 grid((unsigned)(tiles * a.nkv), 1, a.n_rows);
     attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(mq, mkv, a);
     LLME_LAUNCH_STATUS();
 }
