@@ -339,7 +339,9 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
 
         # ---- end to end through the Python entry point: host tokens in, host tokens out, every step
-        ids = [llm.add_request(tokens(CACHED), sp, max_tokens=args.warmup + args.steps + 2, eos_token_id=None)
+        # (a request decodes while the prompts behind it are still being read: room for those tokens too, so that
+        # none ends inside the timed steps)
+        ids = [llm.add_request(tokens(CACHED), sp, max_tokens=args.warmup + args.steps + 2 * args.batch + 8, eos_token_id=None)
                for _ in range(args.batch)]
         while any(llm.scheduler.state(i).phase.value != "decoding" for i in ids):
             llm.step()
