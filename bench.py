@@ -193,7 +193,14 @@ def breakdown(args) -> int:
             ("attention", lambda l: blocks[l].mixer.attend(q, eng._caches[l].kv, ao, batch, grp), 0),
             ("output product", lambda l: ops.linear(ao, blocks[l].mixer.w_o, mo), H * qs),
             ("rmsnorm + residual add (feed-forward)", lambda l: blocks[l].ffn_norm.forward(x, delta=mo), 0),
-            ("gate|up product + swiglu", lambda l: ops.linear_swiglu(h, blocks[l].ffn.w_gate_up, act), 2 * I * H),
+        ]
+        if ops.linear_swiglu_supports(h, blocks[0].ffn.w_gate_up, act):
+            table.append(("gate|up product + swiglu", lambda l: ops.linear_swiglu(h, blocks[l].ffn.w_gate_up, act), 2 * I * H))
+        else:                                  # between 17 and 127 tokens: the library product, then the activation
+            gu = torch.empty(rows, 2 * I, device="cuda", dtype=torch.bfloat16)
+            table.append(("gate|up product", lambda l: ops.linear(h, blocks[l].ffn.w_gate_up, gu), 2 * I * H))
+            table.append(("swiglu", lambda l: ops.swiglu(gu, act), 0))
+        table += [
             ("down product", lambda l: ops.linear(act, blocks[l].ffn.w_down, mo), H * I),
         ]
         out, total = [], 0.0

@@ -285,54 +285,62 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int blk = ps_shift >= 0 ? ja >> ps_shift : ja / ps;
             return (long long)bt[blk] * page_rows + head_rows + (ja - blk * ps);
         };
-        long long next_row = first_row(0);
-        for (int i = 0; i < n_tiles && ok; ++i) {
+        // One load of a tile: its keys (which = 0) or its values (1), into the stage i % 2.
+        auto load_tile = [&](int i, int which, long long my_row) {
             const int s = i & 1, round = i >> 1;
             const int j0 = (tile_first + i) * BN;
-            const long long my_row = next_row;
-            next_row = first_row(i + 1);
             const int ja = j0 + (my_box << box_shift), jb = ja + rows_per_box - 1;
             const bool whole = my_row >= 0 && ja >= lo_min && jb <= hi_max;
             const unsigned whole_mask = __ballot_sync(0xffffffffu, whole);                 // one bit per TMA load
             const unsigned part_mask = __ballot_sync(0xffffffffu, my_row >= 0 && !whole && my_half == 0);
             const unsigned tx = (unsigned)__popc(whole_mask) * load_bytes;
-            for (int which = 0; which < 2 && ok; ++which) {       // keys, then values
-                unsigned long long* empty = which ? &bar->v_empty[s] : &bar->k_empty[s];
-                unsigned long long* full = which ? &bar->v_full[s] : &bar->k_full[s];
-                unsigned char* tile = (which ? v_tiles : k_tiles) + s * TILE_BYTES;
-                ok = mbar_wait(empty, (round & 1) ^ 1, abort_flag, 10 + which) && !*abort_flag;
-                if (!ok) break;
-                if (lane == 0) trace(8 + which, i);
-                // First the boxes that straddle an edge of the visible range: they are copied by hand, visible
-                // rows only, the rest zeroed.  Then, after those writes are published, one lane arms the barrier
-                // and the lanes start the TMA loads of the boxes that are needed whole.
-                if (part_mask) {
-                    for (unsigned rest = part_mask; rest; rest &= rest - 1) {
-                        const int src_lane = __ffs(rest) - 1, b = (src_lane >> H_SHIFT) << box_shift;
-                        const long long row0 = __shfl_sync(0xffffffffu, my_row, src_lane) + (which ? v_rows : 0);
-                        for (int c = lane; c < rows_per_box * (HD / 8); c += 32) {
-                            const int rr = c / (HD / 8), ch = c % (HD / 8);
-                            const int j = j0 + b + rr;
-                            uint4 v = make_uint4(0, 0, 0, 0);
-                            if (j >= lo_min && j <= hi_max) v = *reinterpret_cast<const uint4*>(a.cache + (row0 + rr) * HD + ch * 8);
-                            const int h = ch >> 3, q = ch & 7, row = b + rr;
-                            *reinterpret_cast<uint4*>(tile + h * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) = v;
-                        }
+            unsigned long long* empty = which ? &bar->v_empty[s] : &bar->k_empty[s];
+            unsigned long long* full = which ? &bar->v_full[s] : &bar->k_full[s];
+            unsigned char* tile = (which ? v_tiles : k_tiles) + s * TILE_BYTES;
+            ok = mbar_wait(empty, (round & 1) ^ 1, abort_flag, 10 + which) && !*abort_flag;
+            if (!ok) return;
+            if (lane == 0) trace(8 + which, i);
+            // First the boxes that straddle an edge of the visible range: they are copied by hand, visible
+            // rows only, the rest zeroed.  Then, after those writes are published, one lane arms the barrier
+            // and the lanes start the TMA loads of the boxes that are needed whole.
+            if (part_mask) {
+                for (unsigned rest = part_mask; rest; rest &= rest - 1) {
+                    const int src_lane = __ffs(rest) - 1, b = (src_lane >> H_SHIFT) << box_shift;
+                    const long long row0 = __shfl_sync(0xffffffffu, my_row, src_lane) + (which ? v_rows : 0);
+                    for (int c = lane; c < rows_per_box * (HD / 8); c += 32) {
+                        const int rr = c / (HD / 8), ch = c % (HD / 8);
+                        const int j = j0 + b + rr;
+                        uint4 v = make_uint4(0, 0, 0, 0);
+                        if (j >= lo_min && j <= hi_max) v = *reinterpret_cast<const uint4*>(a.cache + (row0 + rr) * HD + ch * 8);
+                        const int h = ch >> 3, q = ch & 7, row = b + rr;
+                        *reinterpret_cast<uint4*>(tile + h * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) = v;
                     }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                __syncwarp();
-                if (lane == 0) mbar_expect_tx(full, tx);
-                __syncwarp();
-                if (lane == 0) trace(10 + which, i);
-                // every lane starts the loads of its own box: issued from one thread, the many small boxes of
-                // small pages went out one after the other and took longer than the arithmetic on them
-                if (whole)
-                    tma_load_2d(tile + my_half * HALF_BYTES + (my_box << box_shift) * 128, &map_kv, my_half * 64,
-                                (int)(my_row + (which ? v_rows : 0)), full);
-                if (lane == 0) trace(which, i);
-                __syncwarp();
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
+            __syncwarp();
+            if (lane == 0) mbar_expect_tx(full, tx);
+            __syncwarp();
+            if (lane == 0) trace(10 + which, i);
+            // every lane starts the load of its own box: issued from one thread, the many small boxes of
+            // small pages went out one after the other and took longer than the arithmetic on them
+            if (whole)
+                tma_load_2d(tile + my_half * HALF_BYTES + (my_box << box_shift) * 128, &map_kv, my_half * 64,
+                            (int)(my_row + (which ? v_rows : 0)), full);
+            if (lane == 0) trace(which, i);
+            __syncwarp();
+        };
+        // The keys run one tile ahead of the values: K(i+1) only waits for the scores of tile i-1, V(i) for the
+        // output product of tile i-2, which comes a softmax later; in the order K(i), V(i), K(i+1) the keys of the
+        // next tile would queue behind that wait and the matrix warp would stall on them.
+        long long row_cur = first_row(0), row_next = first_row(1);
+        load_tile(0, 0, row_cur);
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const long long row_after = first_row(i + 2);
+            if (i + 1 < n_tiles) load_tile(i + 1, 0, row_next);
+            if (ok) load_tile(i, 1, row_cur);
+            row_cur = row_next;
+            row_next = row_after;
         }
         if (*abort_flag) {
             // gave up somewhere: give the copies that are still in flight time to land before the block exits
@@ -436,17 +444,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar->s_empty[s]);
                 const bool unmasked = warp_full && j0 + BH - 1 <= warp_p_lo && j0 >= warp_lo_last;
-                if (unmasked) {
-#pragma unroll
-                    for (int e = 0; e < BH; ++e) mx = fmaxf(mx, sv[e]);
-                } else {
+                if (!unmasked) {
 #pragma unroll
                     for (int e = 0; e < BH; ++e) {
                         const int j = j0 + e;
                         if (j < plo || j > phi) sv[e] = -INFINITY;
-                        mx = fmaxf(mx, sv[e]);
                     }
                 }
+                // four chains instead of one: the maximum of 64 values is not 64 dependent instructions
+                float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int e = 0; e < BH; e += 4) {
+                    mq[0] = fmaxf(mq[0], sv[e]); mq[1] = fmaxf(mq[1], sv[e + 1]);
+                    mq[2] = fmaxf(mq[2], sv[e + 2]); mq[3] = fmaxf(mq[3], sv[e + 3]);
+                }
+                mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
             }
             // the row's maximum over both halves (a warp that gave up still comes to the barrier: its partner waits there)
             bar->row_max[s][ch][row] = mx;
@@ -481,7 +493,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             m_ref = m_new;
             // probabilities, their sum, and this half of the bfloat16 P tile (row `row`, 16-byte chunk q at q ^ (row % 8))
-            float sum = 0.0f;
+            float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};              // four partial sums, added in a fixed order below
 #pragma unroll
             for (int c = 0; c < BH; c += 8) {
                 unsigned pk[4];
@@ -489,7 +501,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int e = 0; e < 8; e += 2) {
                     const float e0 = fast_exp2(fmaf(sv[c + e], sc, -ref));        // a masked score is -inf: exactly 0
                     const float e1 = fast_exp2(fmaf(sv[c + e + 1], sc, -ref));
-                    sum += e0 + e1;
+                    sq[e >> 1] += e0 + e1;
                     __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
                     pk[e >> 1] = *reinterpret_cast<unsigned*>(&hh);
                 }
@@ -497,7 +509,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 *reinterpret_cast<uint4*>(p_tile + ch * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) =
                     make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
-            l_run += sum;
+            l_run += (sq[0] + sq[1]) + (sq[2] + sq[3]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
