@@ -1,26 +1,33 @@
 // Paged causal attention for prompt portions on the tcgen05 tensor cores of sm_100a (bfloat16, head size
 // HEAD_DIM = 64 or 128, compiled per head size like attention_fast.cu).
 //
-// A block serves one request, one key/value head and 128 rows, a row being a (token, query head of the
-// group) pair.  Keys and values stream through shared memory 128 at a time:
+// A block serves one request, one key/value head and 256 rows, a row being a (token, query head of the
+// group) pair: two Q tiles of 128 rows that share every key/value tile the block loads.  Keys and values
+// stream through shared memory 128 at a time:
 //
-//   warp 0      producer: TMA loads of the Q tile (a 3-D box: tokens x heads of the group x 64 columns) and,
+//   warp 0      producer: TMA loads of the Q tiles (3-D boxes: tokens x heads of the group x 64 columns) and,
 //               page by page through the block table, of the K and V tiles (128-byte swizzle, two stages
-//               each).  A page that holds keys beyond what the tile may see is copied by hand instead, with
-//               those rows zeroed, so that stale memory (NaN included) never reaches the tensor cores.
-//   warp 1      issues the matrix instructions: S = Q K^T (128 x 128 x HEAD_DIM) into one of two score
-//               buffers in tensor memory, and O += P V (128 x HEAD_DIM x 128) into the output accumulator,
-//               also in tensor memory; V is read as an MN-major operand, exactly as it lies in the cache.
-//   warps 2..9  softmax: two threads per row, 64 keys of the tile each (a warp may only touch the 32 lanes of
-//               tensor memory given by its index modulo 4, so warps w and w+4 share the same 32 rows and
-//               split the columns).  They read S from tensor memory (tcgen05.ld), mask by absolute
-//               position, agree on the row's maximum through shared memory, keep the running reference
-//               maximum and their half of the sum in 32-bit, and write the probabilities as bfloat16 into
-//               the swizzled P tile.  The output accumulator stays in tensor memory.
+//               each, one load per lane, the keys one tile ahead of the values).  A page that holds keys
+//               beyond what the block may see is copied by hand instead, with those rows zeroed, so that
+//               stale memory (NaN included) never reaches the tensor cores.
+//   warp 1      issues the matrix instructions, alternating between the two Q tiles so that the tensor pipe
+//               works for one while the softmax of the other runs: S_t = Q_t K^T (128 x 128 x HEAD_DIM) into
+//               the tile's score columns of tensor memory, and O_t += P_t V (128 x HEAD_DIM x 128) into its
+//               output accumulator, also in tensor memory.  P_t is read from tensor memory (it replaces
+//               the scores it was made from); V is read as an MN-major operand, exactly as it lies in the cache.
+//   warps 2..17 softmax, eight warps per Q tile: two threads per row, 64 keys of the tile each (a warp may
+//               only touch the 32 lanes of tensor memory given by its index modulo 4).  Both find the row's
+//               maximum over all 128 scores by themselves, keep a lazily moved reference maximum and their
+//               half of the sum in 32-bit, and store the probabilities as bfloat16 pairs back into tensor
+//               memory (tcgen05.st) over their own scores, after a 64-thread named barrier with the partner.
 //
-// The score of tile i+1 is computed while the softmax of tile i runs, and P V of tile i while the softmax of
-// tile i+1 runs.  Every mbarrier wait is bounded; a wait that gives up sets an error flag (read with
-// llme_attention_tc_status()), and the block drains its copies, frees its tensor memory and returns.
+// Every mbarrier wait is bounded; a wait that gives up sets an error flag (read with
+// llme_attention_tc_status()), and the block drains its copies, frees its tensor memory and returns.  A warp
+// that has given up still attends every named barrier of its pair.
+//
+// Measured (2,048-token prompt, 32 query and 8 key/value heads of 128, B200): 63 us; one Q tile per block with
+// P in shared memory took 71 us, and was bound by the L2 traffic of every block re-reading the keys and values
+// and by the one thread that issues the matrix instructions (about 0.6 us per group of eight).
 //
 // Reference counterpart: flash_sdpa_tiled_kernel (src/runtime/kernels/cuda_kernels.cu:558-645): one block per
 // query row, scalar FMA, keys of the same launch only.
@@ -40,13 +47,14 @@ namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int HD = HEAD_DIM;
 constexpr int HALVES = HD / 64;        // 64-column (128-byte) halves of a row
-constexpr int BM = 128;                // rows per block
+constexpr int BM = 128;                // rows per Q tile
+constexpr int QT = 2;                  // Q tiles per block: they share every key/value tile the block loads
 constexpr int BN = 128;                // keys per tile
 #ifndef LLME_TC_BOX_ROWS
 #define LLME_TC_BOX_ROWS 32
 #endif
 constexpr int BOX_ROWS = LLME_TC_BOX_ROWS;   // most keys one TMA load brings; a tile's loads are started by as many lanes
-constexpr int THREADS = 320;           // producer, matrix warp, eight softmax warps
+constexpr int THREADS = 32 * (2 + 8 * QT);   // producer, matrix warp, eight softmax warps per Q tile
 constexpr int HALF_BYTES = 128 * 128;  // a [128 rows x 64 columns] bfloat16 tile with 128-byte rows
 constexpr int TILE_BYTES = HALVES * HALF_BYTES;
 constexpr unsigned WAIT_LIMIT = 1u << 20;
@@ -86,6 +94,7 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
     for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
@@ -129,12 +138,40 @@ __device__ __forceinline__ unsigned long long desc_mn_major(const void* tile) {
 __host__ __device__ constexpr unsigned idesc(int M, int N, int b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)b_mn << 16) | ((unsigned)(N >> 3) << 17) | ((unsigned)(M >> 4) << 24);
 }
-__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned id, unsigned acc) {
+// The matrix instructions of one group, in one piece of assembly: between two of them nothing but the two
+// additions that move the descriptors on by 16 k values (the issuing thread is alone on its path: every extra
+// instruction of its dependent chain holds both Q tiles up).
+// S = Q K^T over 64 columns of the head (four steps of 16): descriptors + 2 per step (32 bytes inside the swizzled rows).
+template <bool FIRST_NEW>
+__device__ __forceinline__ void umma_qk_half(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned id) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"(acc) : "memory");
+        "{\n\t.reg .pred pn, pa;\n\t.reg .b64 a, b;\n\t"
+        "setp.eq.u32 pn, 1, %4;\n\t"
+        "setp.eq.u32 pa, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pn;\n\t"
+        "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pa;\n\t"
+        "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pa;\n\t"
+        "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pa;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "n"(FIRST_NEW ? 0 : 1) : "memory");
+}
+// O (+)= P V over 64 keys (four steps of 16): P in tensor memory, 8 columns per step; V MN-major, two 1024-byte
+// groups (+ 128 in the descriptor) per step.  `acc_first`: whether the first step adds to what O holds.
+__device__ __forceinline__ void umma_pv_half(unsigned tmem_d, unsigned tmem_p, unsigned long long dv, unsigned id, unsigned acc_first) {
+    asm volatile(
+        "{\n\t.reg .pred pf, pa;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "setp.ne.b32 pf, %4, 0;\n\t"
+        "setp.eq.u32 pa, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pf;\n\t"
+        "add.u32 a, %1, 8;\n\tadd.u64 b, %2, 128;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pa;\n\t"
+        "add.u32 a, %1, 16;\n\tadd.u64 b, %2, 256;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pa;\n\t"
+        "add.u32 a, %1, 24;\n\tadd.u64 b, %2, 384;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pa;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_p), "l"(dv), "r"(id), "r"(acc_first) : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -171,6 +208,19 @@ __device__ __forceinline__ void tmem_st32(unsigned addr, const float (&v)[32]) {
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_st32u(unsigned addr, const unsigned (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(addr),
+          "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -193,39 +243,38 @@ __device__ __forceinline__ void trace(int, int) {}
 
 struct Barriers {
     unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
-    unsigned long long s_full[2], s_empty[2], p_full, p_empty, o_full[2], o_empty[2];
+    unsigned long long s_full[QT], p_full[QT], p_empty[QT], o_full;
     unsigned tmem_base;
     int abort_flag;
-    float row_max[2][2][BM];      // [tile parity][column half][row]: the halves' maxima of a tile
-    float row_sum[2][BM];         // [column half][row]: the halves' sums at the end
+    float row_sum[QT][2][BM];     // the two halves' sums of a row, at the end
 };
 
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, TcAttnArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_tile = smem;                              // HALVES x [128 rows x 128 B]
-    unsigned char* k_tiles = q_tile + TILE_BYTES;              // 2 stages
+    unsigned char* q_tiles = smem;                             // QT x HALVES x [128 rows x 128 B]
+    unsigned char* k_tiles = q_tiles + QT * TILE_BYTES;        // 2 stages
     unsigned char* v_tiles = k_tiles + 2 * TILE_BYTES;         // 2 stages
-    unsigned char* p_tile = v_tiles + 2 * TILE_BYTES;          // 2 x [128 rows x 64 keys]
-    Barriers* bar = reinterpret_cast<Barriers*>(p_tile + 2 * HALF_BYTES);
+    Barriers* bar = reinterpret_cast<Barriers*>(v_tiles + 2 * TILE_BYTES);
     volatile int* abort_flag = &bar->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = a.rows[blockIdx.z];
-    // blockIdx.x = tile * nkv + head: the blocks with the most keys, of all heads, start first
-    const int kvh = (int)(blockIdx.x % (unsigned)a.nkv), tile_index = (int)(blockIdx.x / (unsigned)a.nkv);
+    // blockIdx.x = pair * nkv + head: the blocks with the most keys, of all heads, start first
+    const int kvh = (int)(blockIdx.x % (unsigned)a.nkv), pair_index = (int)(blockIdx.x / (unsigned)a.nkv);
     const int G = a.nh / a.nkv;
     const int q0 = a.cu_q_lens[r];
     const int q_len = a.cu_q_lens[r + 1] - q0;
     const int M = q_len * G;
-    const int m0 = ((M + BM - 1) / BM - 1 - tile_index) * BM;
+    const int m0 = ((M + QT * BM - 1) / (QT * BM) - 1 - pair_index) * (QT * BM);    // first row of the block's first Q tile
     if (m0 < 0) return;
+    const int n_q = m0 + BM < M ? QT : 1;                             // Q tiles of this block that hold rows
     const int start = a.ctx_lens[r] - q_len;
     const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
     const int ps = a.page_size;
-    const int t_lo = m0 / G, t_hi = min(q_len - 1, (m0 + BM - 1) / G);
-    const int hi_max = start + t_hi;                                  // last key any row of the tile sees
+    const int t_lo = m0 / G, t_hi = min(q_len - 1, (m0 + n_q * BM - 1) / G);
+    const int hi_max = start + t_hi;                                  // last key any row of the block sees
     const int lo_min = a.window > 0 ? max(0, start + t_lo - a.window + 1) : 0;
     const int tile_first = lo_min / BN, tile_last = hi_max / BN;
     const int n_tiles = tile_last - tile_first + 1;
@@ -233,13 +282,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (threadIdx.x == 0) {
         mbar_init(&bar->q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bar->k_full[s], 1); mbar_init(&bar->k_empty[s], 1);
-            mbar_init(&bar->v_full[s], 1); mbar_init(&bar->v_empty[s], 1);
-            mbar_init(&bar->s_full[s], 1); mbar_init(&bar->s_empty[s], 8);
-            mbar_init(&bar->o_full[s], 1); mbar_init(&bar->o_empty[s], 8);
+            mbar_init(&bar->k_full[s], 1);
+            mbar_init(&bar->k_empty[s], 1);
+            mbar_init(&bar->v_full[s], 1);
+            mbar_init(&bar->v_empty[s], 1);
         }
-        mbar_init(&bar->p_full, 8);
-        mbar_init(&bar->p_empty, 1);
+        for (int t = 0; t < QT; ++t) {
+            mbar_init(&bar->s_full[t], 1);
+            mbar_init(&bar->p_full[t], 8);          // the eight softmax warps of a Q tile
+            mbar_init(&bar->p_empty[t], 1);
+        }
+        mbar_init(&bar->o_full, 1);
         bar->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -254,21 +307,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = bar->tmem_base;
-    const unsigned tmem_s[2] = {tmem, tmem + 128};
-    const unsigned tmem_o = tmem + 256;
+    // columns: S of Q tile 0, S of Q tile 1, O of Q tile 0, O of Q tile 1
+    const unsigned tmem_s[QT] = {tmem, tmem + 128};
+    const unsigned tmem_o[QT] = {tmem + 256, tmem + 384};
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
-            mbar_expect_tx(&bar->q_full, TILE_BYTES);
-            for (int h = 0; h < HALVES; ++h)
-                tma_load_3d(q_tile + h * HALF_BYTES, &map_q, h * 64, kvh * G, q0 + t_lo, &bar->q_full);
+            mbar_expect_tx(&bar->q_full, (unsigned)(n_q * TILE_BYTES));
+            for (int t = 0; t < n_q; ++t)
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_3d(q_tiles + t * TILE_BYTES + h * HALF_BYTES, &map_q, h * 64, kvh * G, q0 + (m0 + t * BM) / G, &bar->q_full);
         }
-        // Rows one TMA load of the cache brings: a power of two (pages of 8..64 tokens, or 64 rows of a larger
-        // page).  A lane looks after one TMA load of a tile (box lane / HALVES, 64-column half lane % HALVES): it looks up the box's page (one tile ahead of its use, so
-        // that the look-up's latency is not in front of every tile's copies), and decides whether the box is
-        // needed whole (a TMA load), in part (copied by hand), or not at all.  No division in the loop: the
-        // producer's instructions are a dependent chain, and at 1 block per SM nothing hides their latency.
+        // Rows one TMA load of the cache brings: a power of two (pages of 8..32 tokens, or 32 rows of a larger
+        // page).  A lane looks after one TMA load of a tile (box lane / HALVES, 64-column half lane % HALVES): it
+        // looks up the box's page (two tiles ahead of its use, so that the look-up's latency is not in front of
+        // the copies), and decides whether the box is needed whole (a TMA load), in part (copied by hand), or
+        // not at all.  No division in the loop: the producer's instructions are a dependent chain, and nothing
+        // hides their latency.
         const int rows_per_box = ps < BOX_ROWS ? ps : BOX_ROWS;
         const int box_shift = __ffs(rows_per_box) - 1;
         const int n_boxes = BN >> box_shift;
@@ -287,17 +343,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         };
         // One load of a tile: its keys (which = 0) or its values (1), into the stage i % 2.
         auto load_tile = [&](int i, int which, long long my_row) {
-            const int s = i & 1, round = i >> 1;
             const int j0 = (tile_first + i) * BN;
             const int ja = j0 + (my_box << box_shift), jb = ja + rows_per_box - 1;
             const bool whole = my_row >= 0 && ja >= lo_min && jb <= hi_max;
             const unsigned whole_mask = __ballot_sync(0xffffffffu, whole);                 // one bit per TMA load
             const unsigned part_mask = __ballot_sync(0xffffffffu, my_row >= 0 && !whole && my_half == 0);
             const unsigned tx = (unsigned)__popc(whole_mask) * load_bytes;
-            unsigned long long* empty = which ? &bar->v_empty[s] : &bar->k_empty[s];
-            unsigned long long* full = which ? &bar->v_full[s] : &bar->k_full[s];
-            unsigned char* tile = (which ? v_tiles : k_tiles) + s * TILE_BYTES;
-            ok = mbar_wait(empty, (round & 1) ^ 1, abort_flag, 10 + which) && !*abort_flag;
+            unsigned long long* empty = which ? &bar->v_empty[i & 1] : &bar->k_empty[i & 1];
+            unsigned long long* full = which ? &bar->v_full[i & 1] : &bar->k_full[i & 1];
+            unsigned char* tile = (which ? v_tiles : k_tiles) + (i & 1) * TILE_BYTES;
+            const unsigned use = (unsigned)(i >> 1);                                       // how often the stage was filled before
+            ok = mbar_wait(empty, (use & 1) ^ 1, abort_flag, 10 + which) && !*abort_flag;
             if (!ok) return;
             if (lane == 0) trace(8 + which, i);
             // First the boxes that straddle an edge of the visible range: they are copied by hand, visible
@@ -321,7 +377,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_expect_tx(full, tx);
             __syncwarp();
-            if (lane == 0) trace(10 + which, i);
             // every lane starts the load of its own box: issued from one thread, the many small boxes of
             // small pages went out one after the other and took longer than the arithmetic on them
             if (whole)
@@ -331,8 +386,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             __syncwarp();
         };
         // The keys run one tile ahead of the values: K(i+1) only waits for the scores of tile i-1, V(i) for the
-        // output product of tile i-2, which comes a softmax later; in the order K(i), V(i), K(i+1) the keys of the
-        // next tile would queue behind that wait and the matrix warp would stall on them.
+        // output products of tile i-2, which come a softmax later.
         long long row_cur = first_row(0), row_next = first_row(1);
         load_tile(0, 0, row_cur);
         for (int i = 0; i < n_tiles && ok; ++i) {
@@ -348,198 +402,220 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ matrix instructions
+        // Per key tile i and Q tile t: S_t = Q_t K(i)^T, then, when the softmax warps of t have turned S_t into
+        // P_t, O_t += P_t V(i).  The two Q tiles alternate, so that the tensor pipe works for one while the
+        // softmax of the other runs: S_0(0) S_1(0) | O_0(0) S_0(1) O_1(0) S_1(1) | O_0(1) S_0(2) ...
         if (lane == 0) {
             constexpr unsigned id_s = idesc(BM, BN, 0);
             constexpr unsigned id_o = idesc(BM, HD, 1);
             bool ok = mbar_wait(&bar->q_full, 0, abort_flag, 20);
-            auto issue_s = [&](int i) {
+            // The one thread that issues the matrix instructions runs a dependent chain of its own: every
+            // instruction it spends between two products delays both Q tiles (measured: 0.7 us per group of
+            // eight products when the descriptors were built inside the loop, against 0.27 us that the tensor
+            // pipe needs for them).  So the descriptors are built once, and a group is waits, eight
+            // instructions and commits.
+            unsigned long long dq[QT][HALVES], dk[2][HALVES], dv[2];
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+#pragma unroll
+                for (int t = 0; t < QT; ++t) dq[t][h] = desc_k_major(q_tiles + t * TILE_BYTES + h * HALF_BYTES);
+#pragma unroll
+                for (int s = 0; s < 2; ++s) dk[s][h] = desc_k_major(k_tiles + s * TILE_BYTES + h * HALF_BYTES);
+            }
+#pragma unroll
+            for (int s = 0; s < 2; ++s) dv[s] = desc_mn_major(v_tiles + s * TILE_BYTES);
+            auto issue_s = [&](int t, int i) {
                 const int s = i & 1, round = i >> 1;
                 ok = ok && mbar_wait(&bar->k_full[s], round & 1, abort_flag, 21);
-                ok = ok && mbar_wait(&bar->s_empty[s], (round & 1) ^ 1, abort_flag, 22);
                 if (!ok) return;
+                // S_t is free: its last readers finished before they filled P_t(i-1), which O_t(i-1) below waited for
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    const unsigned long long dq = desc_k_major(q_tile + h * HALF_BYTES);
-                    const unsigned long long dk = desc_k_major(k_tiles + s * TILE_BYTES + h * HALF_BYTES);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) umma(tmem_s[s], dq + 2 * k, dk + 2 * k, id_s, (h > 0 || k > 0) ? 1u : 0u);
-                }
-                umma_commit(&bar->k_empty[s]);
-                umma_commit(&bar->s_full[s]);
-                trace(2, i);
+                const unsigned d = t == 0 ? tmem_s[0] : tmem_s[1];
+                umma_qk_half<true>(d, t == 0 ? dq[0][0] : dq[QT - 1][0], s == 0 ? dk[0][0] : dk[1][0], id_s);
+                if (HALVES == 2)
+                    umma_qk_half<false>(d, t == 0 ? dq[0][HALVES - 1] : dq[QT - 1][HALVES - 1], s == 0 ? dk[0][HALVES - 1] : dk[1][HALVES - 1], id_s);
+                if (t == n_q - 1) umma_commit(&bar->k_empty[s]);      // both Q tiles have read K(i)
+                umma_commit(&bar->s_full[t]);
+                trace(2 + t, i);
             };
-            auto issue_o = [&](int i) {
+            auto issue_o = [&](int t, int i) {
                 const int s = i & 1, round = i >> 1;
-                ok = ok && mbar_wait(&bar->p_full, i & 1, abort_flag, 23);
+                ok = ok && mbar_wait(&bar->p_full[t], i & 1, abort_flag, 23);
                 ok = ok && mbar_wait(&bar->v_full[s], round & 1, abort_flag, 24);
                 if (!ok) return;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned long long dv = desc_mn_major(v_tiles + s * TILE_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    // P: 16 keys = 32 bytes further inside the 64-key half; V: 16 keys = two 1024-byte groups further
-                    const unsigned long long dp = desc_k_major(p_tile + (kk >> 2) * HALF_BYTES) + 2 * (kk & 3);
-                    umma(tmem_o, dp, dv + (unsigned long long)(kk * (2048 >> 4)), id_o, (i > 0 || kk > 0) ? 1u : 0u);
+                const unsigned d = t == 0 ? tmem_o[0] : tmem_o[1];
+                const unsigned pa = t == 0 ? tmem_s[0] : tmem_s[1];
+                const unsigned long long b0 = s == 0 ? dv[0] : dv[1];
+                // P lies in tensor memory, over the scores it was made from: the probabilities of keys 0..63 in
+                // columns 0..31 of S_t, those of keys 64..127 in columns 64..95
+                umma_pv_half(d, pa, b0, id_o, i > 0 ? 1u : 0u);
+                umma_pv_half(d, pa + 64u, b0 + 4ull * (2048 >> 4), id_o, 1u);
+                umma_commit(&bar->p_empty[t]);
+                trace(12 + t, i);
+                if (t == n_q - 1) {
+                    umma_commit(&bar->v_empty[s]);                    // both Q tiles have read V(i)
+                    if (i == n_tiles - 1) umma_commit(&bar->o_full);  // the output accumulators are complete
                 }
-                umma_commit(&bar->v_empty[s]);
-                umma_commit(&bar->p_empty);
-                if (i == n_tiles - 1) umma_commit(&bar->o_full[0]);     // the output accumulator is complete
-                trace(3, i);
             };
-            if (ok) issue_s(0);
-            for (int i = 1; i < n_tiles && ok; ++i) {
-                issue_s(i);
-                issue_o(i - 1);
-            }
-            if (ok) issue_o(n_tiles - 1);
+            for (int t = 0; t < n_q && ok; ++t) issue_s(t, 0);
+            for (int i = 0; i < n_tiles && ok; ++i)
+                for (int t = 0; t < n_q && ok; ++t) {
+                    issue_o(t, i);
+                    if (i + 1 < n_tiles && ok) issue_s(t, i + 1);
+                }
         }
     } else {
         // ------------------------------------------------------------------ softmax and output
-        // The output accumulator stays in tensor memory and is added to by the matrix warp tile after tile.
-        // A row's probabilities are taken relative to a reference maximum that is only moved when the true
-        // maximum has grown by more than RESCALE (in base-2 units): the final division by the sum, taken
-        // relative to the same reference, makes the result exact, and moving the reference means a round trip
-        // of the accumulator through registers, which then happens only in the first few tiles.
+        // Warp w may touch the 32 lanes of tensor memory given by w % 4 (a quarter of a Q tile's rows); the four
+        // warps with the same quarter serve (Q tile 0 | 1) x (first | second half of the columns).  Both threads
+        // of a row find the row's maximum over all 128 scores of the tile by themselves (the same loads, the
+        // same arithmetic, the same result: nothing to exchange), then each turns its 64 scores into
+        // probabilities.  The output accumulator stays in tensor memory and is added to by the matrix warp
+        // tile after tile.  A row's probabilities are taken relative to a reference maximum that is only moved
+        // when the true maximum has grown by more than RESCALE (in base-2 units): the final division by the
+        // sum, taken relative to the same reference, makes the result exact, and moving the reference means a
+        // round trip of the accumulator through registers, which then happens only in the first few tiles.
         constexpr float RESCALE = 8.0f;
         constexpr int BH = BN / 2;                           // keys of a tile per thread
         constexpr int OC = HD / 2;                           // columns of the output accumulator per thread
-        const int quarter = warp & 3;                        // the 32 lanes of tensor memory this warp may touch
-        const int ch = (warp - 2) >> 2;                      // which half of the columns it takes
-        const int row = quarter * 32 + lane;                 // this thread's row of the tile
-        const int m = m0 + row;
-        const bool row_ok = m < M;
-        const int p = start + min(m, M - 1) / G;             // its position
-        const int phi = row_ok ? p : -1;
-        const int plo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-        const unsigned lane_off = (unsigned)(quarter * 32) << 16;
-        const float sc = a.scale * LOG2E;
-        // what every row of this warp sees entirely, without a mask
-        const int warp_p_lo = start + min(q_len - 1, (m0 + quarter * 32) / G);
-        const int warp_p_hi = start + min(q_len - 1, (m0 + quarter * 32 + 31) / G);
-        const int warp_lo_last = a.window > 0 ? max(0, warp_p_hi - a.window + 1) : 0;
-        const bool warp_full = m0 + quarter * 32 + 31 < M;
-        // the two warps of a quarter meet at a named barrier of their own (64 threads)
-        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
-        float m_ref = -INFINITY, l_run = 0.0f;
-        bool ok = true;
-        for (int i = 0; i < n_tiles; ++i) {
-            const int s = i & 1, round = i >> 1;
-            const int j0 = (tile_first + i) * BN + ch * BH;      // first key of this thread's half
-            ok = ok && mbar_wait(&bar->s_full[s], round & 1, abort_flag, 30);
-            float sv[BH];
-            float mx = -INFINITY;
-            if (warp == 2 && lane == 0) trace(4, i);
-            if (ok) {
+        const int quarter = warp & 3;
+        const int role = (warp - 2) >> 2;                    // 0..3
+        const int t = role >> 1, ch = role & 1;              // Q tile, half of the columns
+        if (t < n_q) {
+            const int row = quarter * 32 + lane;             // this thread's row of its Q tile
+            const int mt0 = m0 + t * BM;
+            const int m = mt0 + row;
+            const bool row_ok = m < M;
+            const int p = start + min(m, M - 1) / G;         // its position
+            const int phi = row_ok ? p : -1;
+            const int plo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+            const unsigned lane_off = (unsigned)(quarter * 32) << 16;
+            const float sc = a.scale * LOG2E;
+            // what every row of this warp sees entirely, without a mask
+            const int warp_p_lo = start + min(q_len - 1, (mt0 + quarter * 32) / G);
+            const int warp_p_hi = start + min(q_len - 1, (mt0 + quarter * 32 + 31) / G);
+            const int warp_lo_last = a.window > 0 ? max(0, warp_p_hi - a.window + 1) : 0;
+            const bool warp_full = mt0 + quarter * 32 + 31 < M;
+            // the two warps of a (Q tile, quarter) meet at a named barrier of their own (64 threads)
+            auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + t * 4 + quarter) : "memory"); };
+            float m_ref = -INFINITY, l_run = 0.0f;
+            bool ok = true;
+            // (every iteration comes to the pair's named barrier exactly once, also after a wait has given up: the
+            // partner must never be left waiting there)
+            for (int i = 0; i < n_tiles; ++i) {
+                const int j0 = (tile_first + i) * BN;
+                unsigned pk[32];
+                ok = ok && mbar_wait(&bar->s_full[t], i & 1, abort_flag, 30);
+                if (ok) {
+                if (warp == 2 && lane == 0) trace(4, i);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int c = 0; c < BH; c += 32) {
-                    float v[32];
-                    tmem_ld32(tmem_s[s] + lane_off + (unsigned)(ch * BH + c), v);
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) sv[c + e] = v[e];
-                }
-                // the scores are in registers: the buffer may be written again
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar->s_empty[s]);
-                const bool unmasked = warp_full && j0 + BH - 1 <= warp_p_lo && j0 >= warp_lo_last;
-                if (!unmasked) {
-#pragma unroll
-                    for (int e = 0; e < BH; ++e) {
-                        const int j = j0 + e;
-                        if (j < plo || j > phi) sv[e] = -INFINITY;
-                    }
-                }
-                // four chains instead of one: the maximum of 64 values is not 64 dependent instructions
+                const bool unmasked = warp_full && j0 + BN - 1 <= warp_p_lo && j0 >= warp_lo_last;
+                // the row's maximum over the whole tile
                 float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int e = 0; e < BH; e += 4) {
-                    mq[0] = fmaxf(mq[0], sv[e]); mq[1] = fmaxf(mq[1], sv[e + 1]);
-                    mq[2] = fmaxf(mq[2], sv[e + 2]); mq[3] = fmaxf(mq[3], sv[e + 3]);
+                for (int c = 0; c < BN; c += 32) {
+                    float v[32];
+                    tmem_ld32(tmem_s[t] + lane_off + (unsigned)c, v);
+                    if (!unmasked) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const int j = j0 + c + e;
+                            if (j < plo || j > phi) v[e] = -INFINITY;
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4) {
+                        mq[0] = fmaxf(mq[0], v[e]); mq[1] = fmaxf(mq[1], v[e + 1]);
+                        mq[2] = fmaxf(mq[2], v[e + 2]); mq[3] = fmaxf(mq[3], v[e + 3]);
+                    }
                 }
-                mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+                const float m_true = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])) * sc;
+                const bool move = m_true > m_ref + RESCALE || (m_ref == -INFINITY && m_true > -INFINITY);
+                const float m_new = move ? m_true : m_ref;
+                const float ref = m_new == -INFINITY ? 0.0f : m_new;
+                if (i > 0 && __any_sync(0xffffffffu, move)) {
+                    // The accumulator is at rest once P V of the tile before has finished.  Both threads of a row
+                    // take the same decision; each rescales its half of the accumulator's columns.
+                    ok = mbar_wait(&bar->p_empty[t], (i & 1) ^ 1, abort_flag, 31);
+                    if (ok) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const float corr = move ? fast_exp2(m_ref - ref) : 1.0f;
+                        l_run *= corr;
+#pragma unroll 1
+                        for (int c = 0; c < OC; c += 32) {
+                            float v[32];
+                            tmem_ld32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) v[e] *= corr;
+                            tmem_st32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
+                        }
+                    }
+                } else if (move) {
+                    l_run *= fast_exp2(m_ref - ref);                 // first tile: nothing accumulated yet
+                }
+                m_ref = m_new;
+                // Probabilities of this thread's 64 keys, their sum, and the bfloat16 P values, two per 32-bit word:
+                // 32 words that replace the first 32 of the thread's own 64 scores in tensor memory (the matrix
+                // warp reads them from there as its A operand).
+                float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};              // four partial sums, added in a fixed order below
+#pragma unroll
+                for (int c0 = 0; c0 < BH; c0 += 32) {
+                    float v[32];
+                    tmem_ld32(tmem_s[t] + lane_off + (unsigned)(ch * BH + c0), v);
+                    if (!unmasked) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const int j = j0 + ch * BH + c0 + e;
+                            if (j < plo || j > phi) v[e] = -INFINITY;
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float e0 = fast_exp2(fmaf(v[e], sc, -ref));            // a masked score is -inf: exactly 0
+                        const float e1 = fast_exp2(fmaf(v[e + 1], sc, -ref));
+                        sq[(e >> 1) & 3] += e0 + e1;
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
+                        pk[(c0 + e) >> 1] = *reinterpret_cast<unsigned*>(&hh);
+                    }
+                }
+                l_run += (sq[0] + sq[1]) + (sq[2] + sq[3]);
+                }
+                // the partner has finished its pass over all of the row's scores (it read this thread's half too)
+                pair_sync();
+                if (ok) {
+                    tmem_st32u(tmem_s[t] + lane_off + (unsigned)(ch * BH), pk);
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar->p_full[t]);
+                    if (warp == 2 && lane == 0) trace(7, i);
+                }
             }
-            // the row's maximum over both halves (a warp that gave up still comes to the barrier: its partner waits there)
-            bar->row_max[s][ch][row] = mx;
+            if (ok) ok = mbar_wait(&bar->o_full, 0, abort_flag, 33);
+            // the row's sum over both halves
+            bar->row_sum[t][ch][row] = l_run;
             pair_sync();
-            if (!ok || *abort_flag) { ok = false; continue; }
-            if (warp == 2 && lane == 0) trace(5, i);
-            mx = fmaxf(mx, bar->row_max[s][ch ^ 1][row]);
-            const float m_true = mx * sc;
-            const bool move = m_true > m_ref + RESCALE || (m_ref == -INFINITY && m_true > -INFINITY);
-            const float m_new = move ? m_true : m_ref;
-            const float ref = m_new == -INFINITY ? 0.0f : m_new;
-            // the P tile is free, and the accumulator at rest, once P V of the tile before has finished
-            ok = mbar_wait(&bar->p_empty, (i & 1) ^ 1, abort_flag, 31);
-            if (!ok) continue;
-            if (warp == 2 && lane == 0) trace(6, i);
-            if (i > 0 && __any_sync(0xffffffffu, move)) {
-                // both warps of the quarter see the same maxima and take the same decision; each rescales its
-                // half of the accumulator's columns
+            l_run += bar->row_sum[t][ch ^ 1][row];
+            if (ok && !*abort_flag) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const float corr = move ? fast_exp2(m_ref - ref) : 1.0f;
-                l_run *= corr;
+                const float inv = 1.0f / l_run;
+                bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD + ch * OC;
 #pragma unroll 1
                 for (int c = 0; c < OC; c += 32) {
                     float v[32];
-                    tmem_ld32(tmem_o + lane_off + (unsigned)(ch * OC + c), v);
+                    tmem_ld32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
+                    if (row_ok) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] *= corr;
-                    tmem_st32(tmem_o + lane_off + (unsigned)(ch * OC + c), v);
-                }
-            } else if (move) {
-                l_run *= fast_exp2(m_ref - ref);                 // first tile: nothing accumulated yet
-            }
-            m_ref = m_new;
-            // probabilities, their sum, and this half of the bfloat16 P tile (row `row`, 16-byte chunk q at q ^ (row % 8))
-            float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};              // four partial sums, added in a fixed order below
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 pk;
+                            unsigned* pw = reinterpret_cast<unsigned*>(&pk);
 #pragma unroll
-            for (int c = 0; c < BH; c += 8) {
-                unsigned pk[4];
-#pragma unroll
-                for (int e = 0; e < 8; e += 2) {
-                    const float e0 = fast_exp2(fmaf(sv[c + e], sc, -ref));        // a masked score is -inf: exactly 0
-                    const float e1 = fast_exp2(fmaf(sv[c + e + 1], sc, -ref));
-                    sq[e >> 1] += e0 + e1;
-                    __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
-                    pk[e >> 1] = *reinterpret_cast<unsigned*>(&hh);
-                }
-                const int q = c >> 3;                              // chunk index within the 64-key half
-                *reinterpret_cast<uint4*>(p_tile + ch * HALF_BYTES + row * 128 + ((q ^ (row & 7)) << 4)) =
-                    make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
-            l_run += (sq[0] + sq[1]) + (sq[2] + sq[3]);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar->p_full);
-            if (warp == 2 && lane == 0) trace(7, i);
-        }
-        // the row's sum over both halves
-        bar->row_sum[ch][row] = l_run;
-        pair_sync();
-        l_run += bar->row_sum[ch ^ 1][row];
-        if (ok) ok = mbar_wait(&bar->o_full[0], 0, abort_flag, 33);
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = 1.0f / l_run;
-            bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD + ch * OC;
-#pragma unroll 1
-            for (int c = 0; c < OC; c += 32) {
-                float v[32];
-                tmem_ld32(tmem_o + lane_off + (unsigned)(ch * OC + c), v);
-                if (row_ok) {
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 pk;
-                        unsigned* pw = reinterpret_cast<unsigned*>(&pk);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 hh = __floats2bfloat162_rn(v[q4 * 8 + 2 * e] * inv, v[q4 * 8 + 2 * e + 1] * inv);
-                            pw[e] = *reinterpret_cast<unsigned*>(&hh);
+                            for (int e = 0; e < 4; ++e) {
+                                __nv_bfloat162 hh = __floats2bfloat162_rn(v[q4 * 8 + 2 * e] * inv, v[q4 * 8 + 2 * e + 1] * inv);
+                                pw[e] = *reinterpret_cast<unsigned*>(&hh);
+                            }
+                            *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
                         }
-                        *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
                     }
                 }
             }
@@ -566,7 +642,7 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)5 * TILE_BYTES + 2 * HALF_BYTES + sizeof(Barriers) + 64;
+constexpr size_t SMEM_BYTES = 1024 + (size_t)(QT + 4) * TILE_BYTES + sizeof(Barriers) + 64;
 static_assert(SMEM_BYTES <= 232448, "the block's shared memory must fit an SM");
 
 }  // namespace
@@ -627,7 +703,7 @@ LLME_API int llme_attention_tc(const void* q, long long q_tokens, long long tota
         if (e != cudaSuccess) LLME_REFUSE("attention_tc: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    const long long tiles = ((long long)max_q_len * G + BM - 1) / BM;
+    const long long tiles = ((long long)max_q_len * G + QT * BM - 1) / (QT * BM);
     if (tiles * a.nkv > 2147483647LL) LLME_REFUSE("attention_tc: grid too large");
     dim3 grid((unsigned)(tiles * a.nkv), 1, a.n_rows);
     attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(mq, mkv, a);
