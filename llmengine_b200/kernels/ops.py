@@ -11,6 +11,7 @@ package's own FMA kernel.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, byref, c_char_p, c_float, c_int, c_longlong, c_void_p
 from typing import Dict, Optional
 
@@ -100,6 +101,10 @@ class CudaOps:
             raise KernelsUnavailable(f"device {device} is not a CUDA device")
         self._libs: Dict[str, ctypes.CDLL] = {}
         self.use_tcgen05 = True    # products of 128 tokens or more on this package's tcgen05 kernel, else cuBLAS
+        self.plain_gemm = os.environ.get("LLME_GEMM", "auto")   # "auto" | "tcgen05" | "cublas", see _tc_fills_its_waves
+        if self.plain_gemm not in ("auto", "tcgen05", "cublas"):
+            raise KernelError(f"LLME_GEMM must be auto, tcgen05 or cublas, got {self.plain_gemm!r}")
+        self._sms = None
         self.launches = 0          # kernels of this package launched so far (cuBLAS calls are not counted)
 
     # ------------------------------------------------------------------ loading
@@ -315,7 +320,8 @@ class CudaOps:
             self._check(lib, rc, "gemm_skinny")
             return out
         if (self.use_tcgen05 and M >= 128 and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and self._tc_fills_its_waves(M, N)):
             # many tokens: this package's tcgen05 kernel (TMA-fed, accumulator in tensor memory)
             return self.linear_tc(x, w, out)
         if out.dtype == torch.bfloat16:
@@ -323,6 +329,26 @@ class CudaOps:
         else:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         return out
+
+    def _tc_fills_its_waves(self, M: int, N: int) -> bool:
+        """Whether a plain product of this size goes to this package's tcgen05 kernel rather than to cuBLAS.
+
+        The kernel walks over whole 128 x 256 tiles, one block per SM: 256 tiles on 148 SMs take the time of two
+        waves for 1.73 waves of work, and there cuBLAS, which balances such a product, is 10-15 % faster (measured
+        for 2,048 tokens: 70/50/136 us against 81/58/158 us for the q|k|v, output and down products of the 8B
+        shape).  `plain_gemm` = "tcgen05" or "cublas" (or LLME_GEMM in the environment) forces one of them;
+        "auto" takes the kernel when its last wave is at least 90 % full."""
+        if self.plain_gemm != "auto":
+            return self.plain_gemm == "tcgen05"
+        tiles = -(-M // 128) * -(-N // (256 if N > 128 else 128))
+        sms = self._sm_count()
+        waves = -(-tiles // sms)
+        return tiles >= 0.9 * waves * sms
+
+    def _sm_count(self) -> int:
+        if self._sms is None:
+            self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        return self._sms
 
     def skinny_supports(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
         """Whether the weight-streaming kernel for a handful of tokens takes this product."""

@@ -212,6 +212,30 @@ def test_skinny_gemm_with_swiglu(ops, M, inter, K):
     assert ((got - want).abs() <= bound).all()
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(2048, 4096, 4096), (2048, 2560, 520), (1500, 3000, 72), (2048, 6144, 264), (130, 40000, 128)])
+def test_tcgen05_gemm_more_tiles_than_sms(ops, M, N, K, out_dtype):
+    """More tiles than SMs and not a multiple of them: a block walks over several tiles, the last wave is partly
+    empty, both accumulator buffers are in use.  The same bits every time."""
+    a = _rand(M, K, dtype=torch.bfloat16, seed=54)
+    w = _rand(N, K, dtype=torch.bfloat16, seed=55, scale=0.05)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear_tc(a, w, out)
+    assert ops.linear_tc_status() == 0
+    want = (a.double() @ w.double().t()).cpu()
+    got = out.double().cpu()
+    assert torch.isfinite(got).all()
+    tol = 2e-5 * math.sqrt(K) * float(want.abs().max() + 1)
+    if out_dtype == torch.bfloat16:
+        assert ((got - want).abs() <= want.abs() * 2 ** -8 + tol).all()
+    else:
+        assert (got - want).abs().max() < tol
+    for _ in range(2):
+        again = torch.full_like(out, float("nan"))
+        ops.linear_tc(a, w, again)
+        assert torch.equal(again, out)
+
+
 @pytest.mark.parametrize("M,inter,K", [(2048, 12288, 4096), (128, 128, 64), (300, 1000, 264), (129, 72, 520), (1000, 136, 8)])
 def test_tcgen05_gemm_with_swiglu(ops, M, inter, K):
     """The tcgen05 product with the activation in its epilogue against the product followed by the activation
