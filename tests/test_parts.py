@@ -1,6 +1,7 @@
 """Each part of a layer alone against the plain function of the same name, at sizes other than the
-engine tests use; and a toy mixer with state of its own, defined here, that is registered, built
-into a model and stepped without any change to the package."""
+engine tests use; and toy parts defined here (a mixer with state of its own, a feed-forward with
+routing, another position encoding) that are registered, built into models and stepped without any
+change to the package."""
 import math
 
 import pytest
@@ -315,3 +316,171 @@ def test_toy_stateful_mixer_on_the_host():
 @pytest.mark.gpu
 def test_toy_stateful_mixer_registers_builds_and_steps():
     _toy_roundtrip(None, DEV)
+
+
+# ----------------------------------------------------------------------------- a toy feed-forward with routing, a toy position encoding
+@register_part("feed_forward", "toy_top1_experts")
+class ToyTop1Experts(Part):
+    """r = softmax(Wr h) (32-bit), e = argmax r, y = r_e * W2_e relu(W1_e h): every token goes to one of
+    several small two-layer experts.  Plain tensor operations; it exists only to show that a feed-forward
+    with routing plugs in (and that its result does not depend on which other tokens share the step)."""
+
+    capture_safe = False          # gathers rows by expert on the host
+
+    def __init__(self, rt, prefix, hidden_size, inter, experts):
+        super().__init__(rt, prefix)
+        self.hidden, self.inter, self.experts = hidden_size, inter, experts
+        self.router = self.w1 = self.w2 = None
+
+    def weight_specs(self):
+        s = {self.name("router.weight"): WeightSpec((self.experts, self.hidden))}
+        for e in range(self.experts):
+            s[self.name(f"experts.{e}.w1.weight")] = WeightSpec((self.inter, self.hidden))
+            s[self.name(f"experts.{e}.w2.weight")] = WeightSpec((self.hidden, self.inter))
+        return s
+
+    def load_weights(self, t):
+        self.router = t[self.name("router.weight")].float() * 40.0      # (N(0, 0.02) weights: make the choice decisive)
+        self.w1 = [t[self.name(f"experts.{e}.w1.weight")].float() for e in range(self.experts)]
+        self.w2 = [t[self.name(f"experts.{e}.w2.weight")].float() for e in range(self.experts)]
+
+    @staticmethod
+    def route(h, router, w1, w2):
+        r = torch.softmax(h.float() @ router.t(), dim=-1)
+        choice = r.argmax(dim=-1)
+        out = torch.zeros(h.shape[0], w2[0].shape[0], dtype=torch.float32, device=h.device)
+        for e in range(len(w1)):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                y = torch.relu(h[rows].float() @ w1[e].t()) @ w2[e].t()
+                out[rows] = r[rows, e, None] * y
+        return out, choice
+
+    def forward(self, h, batch):
+        return self.route(h, self.router, self.w1, self.w2)[0]
+
+
+@register_part("position", "toy_interleaved_rotation")
+class ToyInterleavedRotation(Part):
+    """Rotates the pairs (2d, 2d+1) of every head by pos * base^(-d): another pairing and another angle than
+    the package's rotary part, applied through the unfused path (no table for the fused kernel)."""
+
+    def __init__(self, rt, prefix, head_dim, base):
+        super().__init__(rt, prefix)
+        self.head_dim, self.base = head_dim, base
+
+    def rotary_table(self):
+        return None
+
+    @staticmethod
+    def rotate(x, positions, head_dim, base):
+        T = x.shape[0]
+        v = x.float().view(T, -1, head_dim // 2, 2)
+        d = torch.arange(head_dim // 2, dtype=torch.float32, device=x.device)
+        ang = positions.to(x.device).float()[:, None] * torch.pow(torch.tensor(float(base), device=x.device), -d)[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = torch.stack([v[..., 0] * c - v[..., 1] * s, v[..., 0] * s + v[..., 1] * c], dim=-1)
+        return out.view(T, -1)
+
+    def apply(self, q, k, positions, num_heads, num_kv_heads):
+        q.copy_(self.rotate(q, positions, self.head_dim, self.base).to(q.dtype))
+        if k is not None:
+            k.copy_(self.rotate(k, positions, self.head_dim, self.base).to(k.dtype))
+
+
+class ToyRoutedConfig(ToyConfig):
+    """Attention with the toy position encoding, and the routed feed-forward in every second layer."""
+
+    ARCHITECTURE = "ToyRoutedForCausalLM"
+
+    def model_spec(self):
+        H, d = self.hidden_size, self.d
+        norm = PartSpec("rmsnorm", {"size": H, "eps": d["eps"]})
+        pos = PartSpec("toy_interleaved_rotation", {"head_dim": d["head_dim"], "base": d["base"]})
+        attn = PartSpec("gqa_attention", {"hidden_size": H, "num_heads": d["heads"], "num_kv_heads": d["kv_heads"],
+                                          "head_dim": d["head_dim"], "qk_norm_eps": d["eps"], "window": 0,
+                                          "position_encoding": pos})
+        dense = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": d["inter"]})
+        routed = PartSpec("toy_top1_experts", {"hidden_size": H, "inter": d["expert_inter"], "experts": d["experts"]})
+        layers = tuple(LayerSpec(f"layers.{i}", PartSpec("prenorm_residual"), attn, norm, f, norm)
+                       for i, f in enumerate((routed, dense, routed)))
+        return ModelSpec(self.ARCHITECTURE, H, self.vocab_size, d["max_positions"],
+                         PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": H}), layers,
+                         tuple(LayerRun(i) for i in range(3)), norm,
+                         PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": H}))
+
+
+if ToyRoutedConfig.ARCHITECTURE not in ARCHITECTURES:
+    register_architecture(ToyRoutedConfig.ARCHITECTURE, ToyRoutedConfig)
+
+TOY_ROUTED = {"architectures": [ToyRoutedConfig.ARCHITECTURE], "vocab_size": 113, "hidden_size": 48, "inter": 56,
+              "eps": 1e-5, "heads": 6, "kv_heads": 2, "head_dim": 16, "base": 50.0, "experts": 3, "expert_inter": 40,
+              "max_positions": 256}
+
+
+def _plain_toy_routed(eng, ids):
+    """Whole-sequence evaluation from the engine's loaded tensors with plain functions; also returns how many
+    tokens every expert of the first layer got."""
+    m = eng.model
+    f = lambda t: t.float().cpu()
+    x = pm.embedding(f(m.embedding.table), ids)
+    T = len(ids)
+    pos = torch.arange(T)
+    counts = None
+    for blk in m.blocks:
+        mx = blk.mixer
+        h = pm.rms_norm(x, f(blk.mixer_norm.gain), blk.mixer_norm.eps)
+        qkv = pm.linear(h, f(mx.w_qkv))
+        q = pm.rms_norm(qkv[:, :mx.q_size].reshape(T * mx.nh, mx.hd), f(mx.q_gain), mx.eps).view(T, -1)
+        k = pm.rms_norm(qkv[:, mx.q_size:mx.q_size + mx.kv_size].reshape(T * mx.nkv, mx.hd), f(mx.k_gain), mx.eps).view(T, -1)
+        v = qkv[:, mx.q_size + mx.kv_size:].view(T, mx.nkv, mx.hd)
+        q = ToyInterleavedRotation.rotate(q, pos, mx.hd, mx.position.base).view(T, mx.nh, mx.hd)
+        k = ToyInterleavedRotation.rotate(k, pos, mx.hd, mx.position.base).view(T, mx.nkv, mx.hd)
+        x = x + pm.linear(pm.attention(q, k, v).reshape(T, -1), f(mx.w_o))
+        h = pm.rms_norm(x, f(blk.ffn_norm.gain), blk.ffn_norm.eps)
+        if isinstance(blk.ffn, ToyTop1Experts):
+            y, choice = ToyTop1Experts.route(h, f(blk.ffn.router), [f(w) for w in blk.ffn.w1], [f(w) for w in blk.ffn.w2])
+            if counts is None:
+                counts = torch.bincount(choice, minlength=blk.ffn.experts)
+            x = x + y
+        else:
+            gu = pm.linear(h, f(blk.ffn.w_gate_up))
+            x = x + pm.linear(pm.swiglu(gu[:, :blk.ffn.inter], gu[:, blk.ffn.inter:]), f(blk.ffn.w_down))
+    return pm.linear(pm.rms_norm(x, f(m.final_norm.gain), m.final_norm.eps), f(m.head.weight)), counts
+
+
+def _toy_routed_roundtrip(ops, device):
+    assert "toy_top1_experts" in registered("feed_forward") and "toy_interleaved_rotation" in registered("position")
+    ec = EngineConfig(dtype="float32", page_size=8, max_cached_tokens=192, max_num_seqs=3, max_num_batched_tokens=128,
+                      device=device, use_cuda_graphs=False)
+    eng = Engine(config=TOY_ROUTED, random_seed=11, engine_config=ec, ops=ops)
+    from helpers import random_ids
+    a, b = random_ids(61, 113, 3), random_ids(40, 113, 4)
+    (want_a, counts), (want_b, _) = _plain_toy_routed(eng, a), _plain_toy_routed(eng, b)
+    assert int((counts > 0).sum()) >= 2, "the routing must use more than one expert for the test to mean anything"
+    got = eng.step([StepEntry("a", a, range(61))], end=["a"]).cpu()
+    assert (got - want_a).abs().max() < 2e-4
+    # portions of a beside b and single tokens: a token's expert and result must not depend on its companions
+    rows_a, rows_b = [], []
+    sched = [(("a", 0, 23),), (("a", 23, 2), ("b", 0, 19)), (("b", 19, 20), ("a", 25, 35)), (("a", 60, 1), ("b", 39, 1))]
+    for step in sched:
+        entries = [StepEntry(r, (a if r == "a" else b)[s:s + n], range(n)) for r, s, n in step]
+        out = eng.step(entries).cpu()
+        o = 0
+        for r, s, n in step:
+            (rows_a if r == "a" else rows_b).append(out[o:o + n].clone())
+            o += n
+    assert (torch.cat(rows_a) - want_a).abs().max() < 2e-4
+    assert (torch.cat(rows_b) - want_b).abs().max() < 2e-4
+    eng.free("a"), eng.free("b")
+    eng.cache.check_invariants()
+
+
+def test_toy_routed_feed_forward_and_position_encoding_on_the_host():
+    from host_ops import HostOps
+    _toy_routed_roundtrip(HostOps(), "cpu")
+
+
+@pytest.mark.gpu
+def test_toy_routed_feed_forward_and_position_encoding_register_build_and_step():
+    _toy_routed_roundtrip(None, DEV)
