@@ -369,7 +369,8 @@ constexpr int COUNTER_WORDS = 65536;
 __device__ __forceinline__ float* partials(const FastAttnArgs& a) { return a.scratch + COUNTER_WORDS; }
 constexpr int SUB = 16;           // keys per sub-tile
 constexpr int PAGE_TAB = 512;     // block-table entries a block keeps in shared memory (longer ranges are read from global memory)
-constexpr int DSTAGES = 3;        // stage buffers per warp (two sub-tiles in flight while one is used); two blocks fit an SM
+constexpr int DSTAGES = 2;        // stage buffers per warp (one sub-tile in flight while one is used; three measured the same)
+constexpr int CL_SLOTS = 48;      // (split, row) partial results a cluster's first block can take in its shared memory
 constexpr int STAGE_ELEMS = 2 * SUB * LDS;   // K rows then V rows
 
 // One warp loads keys [j0, j0+16) (K and V) into its stage buffer; keys outside [lo, hi] become zeros.
@@ -421,6 +422,13 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][LDS]
     bf16* stages = Qs + 16 * LDS;                              // [4 warps][DSTAGES][K 16 rows | V 16 rows][LDS]
     float* red = reinterpret_cast<float*>(stages);             // [4 warps][16 rows][PART], reuses the stages after the loop
+    float* cl_part = reinterpret_cast<float*>(stages + 4 * DSTAGES * STAGE_ELEMS);   // [CL_SLOTS][PART]: written by the other blocks of a cluster
+    // Launched as a cluster of `splits` blocks (one per split of a request and key/value head), the blocks hand
+    // their partial results to the first block through distributed shared memory instead of global memory.
+    unsigned cl_rank, cl_size;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cl_rank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(cl_size));
+    const bool clustered = cl_size > 1;
 
     const int zi = blockIdx.z;
     const int r = a.rows[zi];
@@ -560,6 +568,21 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
                 for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + row) * PART + d];
                 dst[d] = __float2bfloat16_rn(acc * inv);
             }
+        } else if (clustered) {
+            // into the shared memory of the cluster's first block, slot (split, row)
+            const unsigned local = (unsigned)__cvta_generic_to_shared(cl_part + ((size_t)split * rows_here + row) * PART);
+            unsigned remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(local));
+            for (int d = lane; d < HD; d += 32) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + row) * PART + d];
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 4u * (unsigned)d), "f"(acc) : "memory");
+            }
+            if (lane == 0) {
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 4u * (unsigned)HD), "f"(mm) : "memory");
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 4u * (unsigned)(HD + 1)), "f"(ll) : "memory");
+            }
         } else {
             float* dst = partials(a) + (((size_t)zi * a.nh + head) * a.splits + split) * PART;
             for (int d = lane; d < HD; d += 32) {
@@ -575,6 +598,48 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
         }
     }
     if (a.splits == 1) return;
+    if (clustered) {
+        // every block of the cluster comes here (none returns earlier); after the barrier the first block finds
+        // all partial results in its own shared memory and merges them, in the order of the splits
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (cl_rank != 0) return;
+        for (int row = warp; row < rows_here; row += 4) {
+            const int head = kvh * G + g0 + row;
+            const float* src = cl_part + (size_t)row * PART;           // split s at src + s * rows_here * PART
+            const size_t step = (size_t)rows_here * PART;
+            float mm = -INFINITY;
+            for (int s2 = lane; s2 < a.splits; s2 += 32) mm = fmaxf(mm, src[s2 * step + HD]);
+            mm = warp_max(mm);
+            const float ref = mm == -INFINITY ? 0.0f : mm;
+            constexpr int KREGS = (HD + 31) / 32;
+            float ll = 0.0f, w_mine = 0.0f;
+            if (lane < a.splits) {
+                w_mine = exp2f(src[lane * step + HD] - ref);
+                ll = w_mine * src[lane * step + HD + 1];
+            }
+            ll = warp_sum(ll);
+            float acc[KREGS];
+#pragma unroll
+            for (int k = 0; k < KREGS; ++k) acc[k] = 0.0f;
+            for (int s2 = 0; s2 < a.splits; ++s2) {                     // at most 8 splits in a cluster
+                const float w = __shfl_sync(0xffffffffu, w_mine, s2);
+#pragma unroll
+                for (int k = 0; k < KREGS; ++k) {
+                    const int d = lane + 32 * k;
+                    if (d < HD) acc[k] += w * src[s2 * step + d];
+                }
+            }
+            bf16* dst = a.out + ((size_t)t * a.nh + head) * HD;
+            const float inv = 1.0f / ll;
+#pragma unroll
+            for (int k = 0; k < KREGS; ++k) {
+                const int d = lane + 32 * k;
+                if (d < HD) dst[d] = __float2bfloat16_rn(acc[k] * inv);
+            }
+        }
+        return;
+    }
 
     // The block that finishes last for this (request, key/value head) merges the splits.  No block waits
     // for another: each one publishes its partial results, takes a ticket, and only the holder of the last
@@ -643,8 +708,17 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
 }
 
 constexpr size_t PORTION_SMEM = (size_t)(BM + 2 * BN) * LDS * sizeof(bf16);
-constexpr size_t DECODE_SMEM = (size_t)(16 * LDS + 4 * DSTAGES * STAGE_ELEMS) * sizeof(bf16);
+constexpr size_t DECODE_SMEM = (size_t)(16 * LDS + 4 * DSTAGES * STAGE_ELEMS) * sizeof(bf16) + (size_t)CL_SLOTS * PART * sizeof(float);
 static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)4 * DSTAGES * STAGE_ELEMS * sizeof(bf16), "the merge buffer must fit the stage buffers");
+
+// LLME_DECODE_CLUSTER=0: the splits always merge through global memory (for comparisons)
+bool cluster_merge_disabled() {
+    static const bool off = [] {
+        const char* e = getenv("LLME_DECODE_CLUSTER");
+        return e && e[0] == '0';
+    }();
+    return off;
+}
 
 int check_common(const FastAttnArgs& a) {
     if (!a.q || !a.cache || !a.out || !a.rows || !a.cu_q_lens || !a.ctx_lens || !a.table_rows || !a.block_tables)
@@ -699,6 +773,27 @@ LLME_API int llme_attention_decode(const FastAttnArgs* args, cudaStream_t stream
     if ((long long)a.nkv * chunks > 65535) LLME_REFUSE("attention: grid too large");
     dim3 grid(a.splits, a.nkv * chunks, a.n_rows);
     if ((long long)a.n_rows * a.nkv * chunks > COUNTER_WORDS) LLME_REFUSE("attention: more than %d (request, head) pairs in one split launch", COUNTER_WORDS);
+    const int rows_cap = G < 16 ? G : 16;
+    if (a.splits >= 2 && a.splits <= 8 && a.splits * rows_cap <= CL_SLOTS && !cluster_merge_disabled()) {
+        // the splits of a (request, key/value head) as one thread-block cluster: they merge through the first
+        // block's shared memory
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = DECODE_SMEM;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = llme_pdl_enabled() ? 1 : 0;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = (unsigned)a.splits;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        cudaLaunchKernelEx(&cfg, attention_decode_kernel, a);
+        LLME_LAUNCH_STATUS();
+    }
     llme_launch(attention_decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, stream, a);
     LLME_LAUNCH_STATUS();
 }
