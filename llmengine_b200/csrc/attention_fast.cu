@@ -55,6 +55,22 @@ struct FastAttnArgs {
     float scale;
 };
 
+// The decode kernel can take the raw projections instead of finished queries: it then norms and rotates the
+// query heads itself, and the block whose share holds the new token's position does the same for the key head
+// and stores key and value in the cache (what the QK-norm/rotation/cache-write kernel would have done in a
+// launch of its own, src/model/transformer_graph_builder.cpp:224-240).
+struct FusedQkv {
+    const bf16* qkv;             // nullable; [T, (nh + 2 nkv) * HD]: query heads, key heads, value heads
+    long long stride;            // elements between tokens
+    const void* q_gain;          // nullable: no norm; [HD]
+    const void* k_gain;
+    int gain_dtype;              // LLME_F32 or LLME_BF16
+    float eps;
+    const float* cos_sin;        // nullable: no rotation; [max_positions, HD] = cos | sin
+    int max_positions;
+    int write_kv;                // 0: the layer reads another layer's cache and stores nothing
+};
+
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
 // 16-byte asynchronous copy; with valid == false the destination is filled with zeros.
@@ -415,7 +431,75 @@ __device__ __forceinline__ void load_sub_tile(bf16* dst, const bf16* cache, cons
     }
 }
 
-__global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs a) {
+// One head (HD values at src) through the per-head RMS norm and the rotate-half rotation, as the kernel of
+// elementwise.cu does it (the same order of operations): lane l holds the pairs (d, d+1) and (d + HD/2, d + HD/2 + 1)
+// for d = 2 (l + 32 i).  The result goes to dst_a and, if given, dst_b.  One warp.
+__device__ __forceinline__ void norm_rotate_head(const bf16* src, const void* gain, int gain_dtype, float eps,
+                                                 const float* cs, bf16* dst_a, bf16* dst_b) {
+    constexpr int half = HD / 2;
+    constexpr int NP = (half + 63) / 64;
+    const int lane = threadIdx.x & 31;
+    float2 lo[NP], hi[NP];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+        const int d = 2 * (lane + 32 * i);
+        if (d < half) {
+            lo[i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + d));
+            hi[i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + d + half));
+            ss += lo[i].x * lo[i].x + lo[i].y * lo[i].y + hi[i].x * hi[i].x + hi[i].y * hi[i].y;
+        }
+    }
+    if (gain) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rinv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const int d = 2 * (lane + 32 * i);
+            if (d < half) {
+                float2 g0, g1;
+                if (gain_dtype == LLME_F32) {
+                    g0 = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(gain) + d);
+                    g1 = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(gain) + d + half);
+                } else {
+                    g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(gain) + d));
+                    g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(gain) + d + half));
+                }
+                lo[i].x = (lo[i].x * rinv) * g0.x; lo[i].y = (lo[i].y * rinv) * g0.y;
+                hi[i].x = (hi[i].x * rinv) * g1.x; hi[i].y = (hi[i].y * rinv) * g1.y;
+            }
+        }
+    }
+    if (cs) {
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const int d = 2 * (lane + 32 * i);
+            if (d < half) {
+                const float2 c = *reinterpret_cast<const float2*>(cs + d);
+                const float2 sn = *reinterpret_cast<const float2*>(cs + half + d);
+                const float2 x0 = lo[i], x1 = hi[i];
+                lo[i] = make_float2(x0.x * c.x - x1.x * sn.x, x0.y * c.y - x1.y * sn.y);
+                hi[i] = make_float2(x0.x * sn.x + x1.x * c.x, x0.y * sn.y + x1.y * c.y);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+        const int d = 2 * (lane + 32 * i);
+        if (d < half) {
+            const __nv_bfloat162 a2 = __floats2bfloat162_rn(lo[i].x, lo[i].y), b2 = __floats2bfloat162_rn(hi[i].x, hi[i].y);
+            *reinterpret_cast<__nv_bfloat162*>(dst_a + d) = a2;
+            *reinterpret_cast<__nv_bfloat162*>(dst_a + d + half) = b2;
+            if (dst_b) {
+                *reinterpret_cast<__nv_bfloat162*>(dst_b + d) = a2;
+                *reinterpret_cast<__nv_bfloat162*>(dst_b + d + half) = b2;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs a, FusedQkv f) {
     // (the next kernel is let in just before the merge below, not here: it would compete with the key/value stream)
     pdl_wait();                // everything below reads or writes what earlier kernels touch
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -472,9 +556,36 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
             __syncthreads();
         }
     }
+    const float* cs_row = nullptr;
+    if (f.qkv && f.cos_sin) {
+        const int pos = p < 0 ? 0 : (p >= f.max_positions ? f.max_positions - 1 : p);      // the host refuses such positions
+        cs_row = f.cos_sin + (size_t)pos * HD;
+    }
+    // this block's share holds the new token's position: it stores the token's key and value
+    const bool writer = f.qkv && f.write_kv && my_first <= my_last && my_last == sub_last;
+    auto store_new_kv = [&]() {
+        const int blk = p / ps;
+        const size_t at = ((((size_t)bt[blk] * 2) * a.nkv + kvh) * ps + (p - blk * ps)) * HD;
+        const bf16* tok = f.qkv + (size_t)t * f.stride;
+        if (warp == 0)
+            norm_rotate_head(tok + (size_t)(a.nh + kvh) * HD, f.k_gain, f.gain_dtype, f.eps, cs_row,
+                             const_cast<bf16*>(a.cache) + at, nullptr);
+        if (warp == 1) {
+            const bf16* vsrc = tok + (size_t)(a.nh + a.nkv + kvh) * HD;
+            bf16* vdst = const_cast<bf16*>(a.cache) + at + (size_t)a.nkv * ps * HD;
+            for (int d = 2 * lane; d < HD; d += 64) *reinterpret_cast<unsigned*>(vdst + d) = *reinterpret_cast<const unsigned*>(vsrc + d);
+        }
+    };
+    // With few sub-tiles the first loads below may already fetch the new token's position: then it is stored first.
+    const bool store_early = writer && my_last - my_first < 4 * (DSTAGES - 1);
+    if (store_early) {
+        store_new_kv();
+        __threadfence_block();
+        __syncthreads();
+    }
     if (my_first <= my_last) {
         // the query rows, loaded by the whole block
-        {
+        if (!f.qkv) {
             constexpr int CHUNKS = HD / 8;
             for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
                 const int row = c / CHUNKS, ch = c - row * CHUNKS;
@@ -483,8 +594,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
                 if (valid) src = a.q + ((size_t)t * a.nh + kvh * G + g0 + row) * HD + ch * 8;
                 cp_async_16(Qs + row * LDS + ch * 8, src, valid);
             }
-            cp_async_commit();
         }
+        cp_async_commit();
         bf16* mine = stages + (size_t)warp * DSTAGES * STAGE_ELEMS;
         // prologue: the first DSTAGES-1 sub-tiles of this warp
 #pragma unroll
@@ -492,6 +603,21 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
             const int sub = my_first + warp + 4 * st;
             if (sub <= my_last) load_sub_tile(mine + st * STAGE_ELEMS, a.cache, tab, tab_first, kvh, a.nkv, ps, page_shift, sub * SUB, lo, p);
             cp_async_commit();
+        }
+        if (f.qkv) {
+            // the query heads from the raw projection: a warp per head; rows beyond the group's heads are zeros
+            for (int row = warp; row < 16; row += 4) {
+                if (row < rows_here)
+                    norm_rotate_head(f.qkv + (size_t)t * f.stride + (size_t)(kvh * G + g0 + row) * HD, f.q_gain, f.gain_dtype, f.eps,
+                                     cs_row, Qs + row * LDS, nullptr);
+                else
+                    for (int d = 2 * lane; d < HD; d += 64) *reinterpret_cast<unsigned*>(Qs + row * LDS + d) = 0u;
+            }
+            // the new token's key and value, before any load that may fetch them (those follow the barrier below)
+            if (writer && !store_early) {
+                store_new_kv();
+                __threadfence_block();
+            }
         }
         cp_async_wait<DSTAGES - 1>();                       // the query rows have landed
         __syncthreads();
@@ -720,8 +846,8 @@ bool cluster_merge_disabled() {
     return off;
 }
 
-int check_common(const FastAttnArgs& a) {
-    if (!a.q || !a.cache || !a.out || !a.rows || !a.cu_q_lens || !a.ctx_lens || !a.table_rows || !a.block_tables)
+int check_common(const FastAttnArgs& a, bool fused = false) {
+    if ((!a.q && !fused) || !a.cache || !a.out || !a.rows || !a.cu_q_lens || !a.ctx_lens || !a.table_rows || !a.block_tables)
         LLME_REFUSE("attention: null pointer");
     if (a.nh <= 0 || a.nkv <= 0 || a.nh % a.nkv) LLME_REFUSE("attention: %d query heads are not a multiple of %d key/value heads", a.nh, a.nkv);
     if (a.page_size <= 0 || a.max_blocks <= 0) LLME_REFUSE("attention: non-positive size");
@@ -756,10 +882,9 @@ LLME_API int llme_attention_portion(const FastAttnArgs* args, int max_q_len, cud
     LLME_LAUNCH_STATUS();
 }
 
-LLME_API int llme_attention_decode(const FastAttnArgs* args, cudaStream_t stream) {
-    const FastAttnArgs& a = *args;
+static int launch_decode(const FastAttnArgs& a, const FusedQkv& f, cudaStream_t stream) {
     if (a.n_rows <= 0) return 0;
-    if (int rc = check_common(a)) return rc;
+    if (int rc = check_common(a, f.qkv != nullptr)) return rc;
     if (a.splits < 1 || a.splits > 1024) LLME_REFUSE("attention: splits must be in 1..1024, got %d", a.splits);
     if (a.splits > 1 && !a.scratch) LLME_REFUSE("attention: split decoding needs scratch memory");
     static bool configured = false;
@@ -791,9 +916,29 @@ LLME_API int llme_attention_decode(const FastAttnArgs* args, cudaStream_t stream
         attr[1].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 2;
-        cudaLaunchKernelEx(&cfg, attention_decode_kernel, a);
+        cudaLaunchKernelEx(&cfg, attention_decode_kernel, a, f);
         LLME_LAUNCH_STATUS();
     }
-    llme_launch(attention_decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, stream, a);
+    llme_launch(attention_decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, stream, a, f);
     LLME_LAUNCH_STATUS();
+}
+
+LLME_API int llme_attention_decode(const FastAttnArgs* args, cudaStream_t stream) {
+    const FusedQkv none = {};
+    return launch_decode(*args, none, stream);
+}
+
+// The same with the raw q|k|v projections of the new tokens instead of finished queries (args->q is ignored):
+// the kernel norms and rotates the heads and stores the new keys and values itself.
+LLME_API int llme_attention_decode_fused(const FastAttnArgs* args, const FusedQkv* fused, cudaStream_t stream) {
+    const FusedQkv& f = *fused;
+    if (!f.qkv) LLME_REFUSE("attention: the fused decode needs the raw projections");
+    if (HD % 4) LLME_REFUSE("attention: the fused decode needs a head size that is a multiple of 4");
+    if (f.stride % 2 || ((uintptr_t)f.qkv | (uintptr_t)f.q_gain | (uintptr_t)f.k_gain | (uintptr_t)f.cos_sin) % 8)
+        LLME_REFUSE("attention: the fused decode needs 8-byte aligned rows");
+    if ((f.q_gain || f.k_gain) && !(f.eps > 0.0f)) LLME_REFUSE("attention: eps must be positive");
+    if ((f.q_gain == nullptr) != (f.k_gain == nullptr)) LLME_REFUSE("attention: the fused decode norms both queries and keys or neither");
+    if (f.q_gain && f.gain_dtype != LLME_F32 && f.gain_dtype != LLME_BF16) LLME_REFUSE("attention: unsupported gain dtype %d", f.gain_dtype);
+    if (f.cos_sin && f.max_positions <= 0) LLME_REFUSE("attention: rotation needs the table's length");
+    return launch_decode(*args, f, stream);
 }

@@ -72,6 +72,13 @@ class _FastAttnArgs(Structure):
     ]
 
 
+class _FusedQkv(Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("stride", c_longlong), ("q_gain", c_void_p), ("k_gain", c_void_p), ("gain_dtype", c_int),
+        ("eps", c_float), ("cos_sin", c_void_p), ("max_positions", c_int), ("write_kv", c_int),
+    ]
+
+
 class _TcAttnArgs(Structure):
     _fields_ = [
         ("out", c_void_p), ("cache", c_void_p), ("rows", c_void_p), ("cu_q_lens", c_void_p), ("ctx_lens", c_void_p),
@@ -283,6 +290,29 @@ class CudaOps:
                             num_kv_heads, page_size, window, scale, splits, scratch)
         rc = lib.llme_attention_decode(byref(a), self._stream())
         self._check(lib, rc, "attention_decode")
+
+    def attention_decode_fused(self, *, qkv, q_gain, k_gain, eps: float, cos_sin, write_kv: bool, cache, out, rows,
+                               cu_q_lens, ctx_lens, table_rows, block_tables, num_heads: int, num_kv_heads: int,
+                               head_dim: int, page_size: int, window: int, scale: float, splits: int,
+                               scratch: Optional[torch.Tensor]) -> None:
+        """attention_decode() on the raw q|k|v projections `qkv` [T, (nh + 2 nkv) * hd] (or [T, nh * hd] when nothing
+        is stored): the kernel norms and rotates the heads itself and, if `write_kv`, stores the new keys and
+        values in the cache before it attends."""
+        lib = self._fast_lib(head_dim)
+        if splits > 1:
+            need = self.attention_decode_scratch_floats(head_dim, rows.numel(), num_heads, splits)
+            assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need
+        assert qkv.dtype == cache.dtype == out.dtype == torch.bfloat16 and qkv.stride(1) == 1 and out.is_contiguous()
+        assert block_tables.is_contiguous() and cache.is_contiguous()
+        assert (q_gain is None) == (k_gain is None) and (q_gain is None or q_gain.dtype == k_gain.dtype)
+        a = _FastAttnArgs(None, cache.data_ptr(), out.data_ptr(), rows.data_ptr(), cu_q_lens.data_ptr(),
+                          ctx_lens.data_ptr(), table_rows.data_ptr(), block_tables.data_ptr(), _ptr(scratch),
+                          block_tables.shape[1], rows.numel(), num_heads, num_kv_heads, page_size, window, splits, scale)
+        f = _FusedQkv(qkv.data_ptr(), qkv.stride(0), _ptr(q_gain), _ptr(k_gain),
+                      _code(q_gain.dtype) if q_gain is not None else 0, float(eps or 0.0), _ptr(cos_sin),
+                      cos_sin.shape[0] if cos_sin is not None else 0, 1 if write_kv else 0)
+        rc = lib.llme_attention_decode_fused(byref(a), byref(f), self._stream())
+        self._check(lib, rc, "attention_decode_fused")
 
     def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         lib = self._lib("elementwise")

@@ -78,8 +78,25 @@ class GQAttention(Part):
         q_in = qkv[:, :qs]
         k_in = qkv[:, qs:qs + kvs] if writes else None
         v_in = qkv[:, qs + kvs:] if writes else None
-        q = rt.buffer("q", T, qs, rt.dtype)
         table = self.position.rotary_table()
+        out = rt.buffer("attn_out", T, qs, rt.dtype)
+        if self._decode_fused(batch, table, T):
+            # a step of single new tokens: norm, rotation and cache write happen inside the attention kernel
+            n_dec = batch.decode_rows.numel()
+            splits = self.decode_splits(n_dec, batch.max_decode_ctx)
+            scratch = None
+            if splits > 1:
+                need = ops.attention_decode_scratch_floats(self.hd, n_dec, self.nh, splits)
+                scratch = rt.buffer("attention_scratch", 1, need, torch.float32, exact=True, zero=True)   # its counters start at zero
+            ops.attention_decode_fused(qkv=qkv, q_gain=self.q_gain, k_gain=self.k_gain, eps=self.eps or 0.0, cos_sin=table,
+                                       write_kv=writes, cache=cache.kv, out=out, rows=batch.decode_rows,
+                                       cu_q_lens=batch.cu_q_lens, ctx_lens=batch.ctx_lens, table_rows=batch.state_slots,
+                                       block_tables=group.block_tables, num_heads=self.nh, num_kv_heads=self.nkv,
+                                       head_dim=self.hd, page_size=group.page_size, window=self.window, scale=self.scale,
+                                       splits=splits, scratch=scratch)
+            delta = rt.buffer("mixer_out", T, self.hidden, torch.float32)
+            return ops.linear(out, self.w_o, delta)
+        q = rt.buffer("q", T, qs, rt.dtype)
         norm = dict(q_gain=self.q_gain, k_gain=self.k_gain, eps=self.eps or 0.0)
         common = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.hd)
         if table is not None:
@@ -94,10 +111,21 @@ class GQAttention(Part):
             if writes:
                 ops.qkv_post(q_in=None, k_in=k, v_in=v_in, **common, cache=cache.kv,
                              slot_mapping=group.slot_mapping, page_size=group.page_size)
-        out = rt.buffer("attn_out", T, qs, rt.dtype)
         self.attend(q, cache.kv, out, batch, group)
         delta = rt.buffer("mixer_out", T, self.hidden, torch.float32)
         return ops.linear(out, self.w_o, delta)
+
+    def _decode_fused(self, batch, table, T: int) -> bool:
+        """Whether this step's attention can take the raw projections: the tensor-core kernels serve this head
+        size, every request brings exactly one token, and the position encoding is either the rotary table or
+        none at all (a part with an `apply` of its own needs the unfused path)."""
+        rt, ops = self.rt, self.rt.ops
+        if not (rt.kernels == "fast" and hasattr(ops, "attention_decode_fused") and hasattr(ops, "fast_attention_supports")
+                and ops.fast_attention_supports(self.hd, rt.dtype)):
+            return False
+        if batch.portion_rows.numel() or batch.decode_rows.numel() != T:
+            return False
+        return table is not None or not getattr(self.position, "needs_apply", True)
 
     def attend(self, q, kv, out, batch, group) -> None:
         """Attention of every token of the batch over its request's cache.  bfloat16 with head sizes

@@ -57,6 +57,8 @@ class RotaryEncoding(Part):
 class NoPositionEncoding(Part):
     """Queries and keys are used as they are."""
 
+    needs_apply = False           # nothing to do for queries and keys: a fused kernel may skip `apply`
+
     def __init__(self, rt: Runtime, prefix: str, **_ignored):
         super().__init__(rt, prefix)
 

@@ -489,6 +489,72 @@ def test_attention_decode_any_number_of_splits(ops, splits):
     assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("splits", [1, 4, 16])
+@pytest.mark.parametrize("hd,page,norm,rope", [(128, 64, "bf16", True), (64, 16, "f32", True), (128, 16, None, True),
+                                               (32, 8, "bf16", False), (128, 128, None, False)])
+def test_attention_decode_on_raw_projections(ops, hd, page, norm, rope, splits):
+    """The decode kernel that norms, rotates and stores the new token's heads itself, against the kernel of
+    elementwise.cu followed by the decode kernel: the same cache contents (to the last bfloat16 digit or one
+    off, where a fused multiply-add rounds differently) and the same outputs."""
+    from llmengine_b200.parts.position import RotaryEncoding
+    nh, nkv = 8, 2
+    ctx_lens = [1, 17, page, page + 1, 300, 64]
+    R = len(ctx_lens)
+    g = torch.Generator().manual_seed(77)
+    blocks = [-(-c // page) for c in ctx_lens]
+    num_pages = sum(blocks) + 2
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    tables = torch.zeros(R, max(blocks) + 1, dtype=torch.int32)
+    cache = torch.full((num_pages, 2, nkv, page, hd), float("nan"))
+    slots = []
+    for r, c in enumerate(ctx_lens):
+        for b in range(blocks[r]):
+            tables[r, b] = perm.pop()
+        for j in range(c - 1):                                   # everything but the new token is in the cache
+            cache[tables[r, j // page], :, :, j % page] = torch.randn(2, nkv, hd, generator=g)
+        slots.append(int(tables[r, (c - 1) // page]) * page + (c - 1) % page)
+    cache = cache.to(torch.bfloat16).to(DEV)
+    qkv = torch.randn(R, (nh + 2 * nkv) * hd, generator=g).to(torch.bfloat16).to(DEV)
+    gains = None
+    if norm:
+        dt = torch.bfloat16 if norm == "bf16" else torch.float32
+        gains = [(1 + 0.1 * torch.randn(hd, generator=g)).to(dt).to(DEV) for _ in range(2)]
+    table = RotaryEncoding.build_table(hd, 10000.0, 512).to(DEV) if rope else None
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, slot_mapping = dev([c - 1 for c in ctx_lens]), dev(slots)
+    meta = dict(rows=dev(list(range(R))), cu_q_lens=dev(list(range(R + 1))), ctx_lens=dev(ctx_lens), table_rows=dev(list(range(R))),
+                block_tables=tables.to(DEV), num_heads=nh, num_kv_heads=nkv, head_dim=hd, page_size=page, window=0,
+                scale=1 / math.sqrt(hd), splits=splits)
+    need = ops.attention_decode_scratch_floats(hd, R, nh, splits) if splits > 1 else 1
+    qs, kvs = nh * hd, nkv * hd
+    # two kernels
+    cache_a, q = cache.clone(), torch.empty(R, qs, dtype=torch.bfloat16, device=DEV)
+    ops.qkv_post(q_in=qkv[:, :qs], k_in=qkv[:, qs:qs + kvs], v_in=qkv[:, qs + kvs:], num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                 q_gain=gains[0] if gains else None, k_gain=gains[1] if gains else None, eps=1e-6 if gains else 0.0,
+                 cos_sin=table, positions=positions, q_out=q, cache=cache_a, slot_mapping=slot_mapping, page_size=page)
+    out_a = torch.full((R, qs), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode(q=q, cache=cache_a, out=out_a, scratch=torch.zeros(need, device=DEV) if splits > 1 else None, **meta)
+    # one kernel
+    cache_b = cache.clone()
+    out_b = torch.full((R, qs), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode_fused(qkv=qkv, q_gain=gains[0] if gains else None, k_gain=gains[1] if gains else None,
+                               eps=1e-6 if gains else 0.0, cos_sin=table, write_kv=True, cache=cache_b, out=out_b,
+                               scratch=torch.zeros(need, device=DEV) if splits > 1 else None, **meta)
+    a, b = cache_a.float().cpu(), cache_b.float().cpu()
+    assert torch.equal(torch.isnan(a), torch.isnan(b)), "exactly the new tokens' rows are written"
+    a, b = torch.nan_to_num(a), torch.nan_to_num(b)
+    assert ((a - b).abs() <= a.abs() * 2 ** -7 + 1e-6).all()
+    assert torch.isfinite(out_b.float()).all()
+    assert (out_a.float() - out_b.float()).abs().max() < 2e-2
+    # nothing is stored when the layer reads another layer's cache
+    cache_c = cache_a.clone()
+    ops.attention_decode_fused(qkv=qkv[:, :qs], q_gain=gains[0] if gains else None, k_gain=gains[1] if gains else None,
+                               eps=1e-6 if gains else 0.0, cos_sin=table, write_kv=False, cache=cache_c, out=out_b,
+                               scratch=torch.zeros(need, device=DEV) if splits > 1 else None, **meta)
+    assert torch.equal(torch.nan_to_num(cache_c.float()), torch.nan_to_num(cache_a.float()))
+    assert (out_a.float() - out_b.float()).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("q_len", [1, 40])
 @pytest.mark.parametrize("where", ["far_back", "page_last", "page_first", "tile_last", "tile_first", "window_inside",
                                    "window_outside"])
