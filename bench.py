@@ -186,11 +186,30 @@ def breakdown(args) -> int:
                          cos_sin=m.position.rotary_table(), positions=batch.positions, q_out=q,
                          cache=eng._caches[l].kv, slot_mapping=grp.slot_mapping, page_size=grp.page_size)
 
+        def fused_attention(l):
+            m = blocks[l].mixer
+            n_dec = batch.decode_rows.numel()
+            splits = m.decode_splits(n_dec, batch.max_decode_ctx)
+            scratch = None
+            if splits > 1:
+                need = ops.attention_decode_scratch_floats(hd, n_dec, nh, splits)
+                scratch = eng.rt.buffer("attention_scratch", 1, need, torch.float32, exact=True, zero=True)
+            ops.attention_decode_fused(qkv=qkv, q_gain=m.q_gain, k_gain=m.k_gain, eps=m.eps, cos_sin=m.position.rotary_table(),
+                                       write_kv=True, cache=eng._caches[l].kv, out=ao, rows=batch.decode_rows,
+                                       cu_q_lens=batch.cu_q_lens, ctx_lens=batch.ctx_lens, table_rows=batch.state_slots,
+                                       block_tables=grp.block_tables, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                                       page_size=grp.page_size, window=0, scale=m.scale, splits=splits, scratch=scratch)
+
         table = [
             ("rmsnorm + residual add (attention)", lambda l: blocks[l].mixer_norm.forward(x, delta=delta), 0),
             ("q|k|v product", lambda l: ops.linear(h, blocks[l].mixer.w_qkv, qkv), (qs + 2 * kvs) * H),
-            ("qk norm + rope + cache write", post, 0),
-            ("attention", lambda l: blocks[l].mixer.attend(q, eng._caches[l].kv, ao, batch, grp), 0),
+        ]
+        if graph:       # a decode step: norm, rotation and cache write happen inside the attention kernel
+            table.append(("qk norm + rope + cache write + attention", fused_attention, 0))
+        else:
+            table.append(("qk norm + rope + cache write", post, 0))
+            table.append(("attention", lambda l: blocks[l].mixer.attend(q, eng._caches[l].kv, ao, batch, grp), 0))
+        table += [
             ("output product", lambda l: ops.linear(ao, blocks[l].mixer.w_o, mo), H * qs),
             ("rmsnorm + residual add (feed-forward)", lambda l: blocks[l].ffn_norm.forward(x, delta=mo), 0),
         ]

@@ -561,7 +561,8 @@ __global__ void swiglu_kernel(const I* __restrict__ in, O* __restrict__ out, lon
         const int i = (int)(idx - t * inter);
         const float g = to_f32(in[t * 2 * inter + i]);
         const float u = to_f32(in[t * 2 * inter + inter + i]);
-        out[idx] = from_f32<O>((g / (1.0f + expf(-g))) * u);
+        if (sizeof(I) == 2) out[idx] = from_f32<O>(silu_mul_bf16(g, u));
+        else out[idx] = from_f32<O>((g / (1.0f + expf(-g))) * u);
     }
 }
 
@@ -581,7 +582,7 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-        o2[k] = __floats2bfloat162_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
+        o2[k] = __floats2bfloat162_rn(silu_mul_bf16(g.x, u.x), silu_mul_bf16(g.y, u.y));
     }
     *reinterpret_cast<uint4*>(out + t * inter + c) = ov;
 }

@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
             if (tok < a.M && col < a.inter) {
                 const float g = __bfloat162float(__float2bfloat16_rn(total(tok * 16 + j)));
                 const float up = __bfloat162float(__float2bfloat16_rn(total(tok * 16 + j + 8)));
-                reinterpret_cast<O*>(a.out)[(size_t)tok * a.ldo + col] = from_f32<O>((g / (1.0f + expf(-g))) * up);
+                reinterpret_cast<O*>(a.out)[(size_t)tok * a.ldo + col] = from_f32<O>(silu_mul_bf16(g, up));
             }
         }
     }

@@ -273,7 +273,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         for (int j = 0; j < 32; ++j) {
                             const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j])));
                             const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j])));
-                            v[j] = __float_as_uint((g / (1.0f + expf(-g))) * u);
+                            v[j] = __float_as_uint(silu_mul_bf16(g, u));
                         }
                     } else {
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
