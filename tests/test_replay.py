@@ -70,8 +70,9 @@ def _traces(reqs):
     }
 
 
-def _run_all(tmp_path, name, dtype, sharpen, ops, device):
+def _run_all(tmp_path, name, dtype, sharpen, ops, device, page_size=None):
     d, page, reqs, ref, tol = _setup(tmp_path, name, dtype, sharpen)
+    page = page_size or page
     worst = {}
     for what, steps in _traces(reqs).items():
         pool = max_live_tokens(steps, 64)
@@ -98,6 +99,16 @@ def test_replay_gpu(tmp_path, name, dtype, sharpen):
     read from a wrong page or seen through a wrong mask moves the logits by far more than the tolerance."""
     worst = _run_all(tmp_path, name, dtype, sharpen, None, "cuda:0")
     print(f"replay {name} {dtype} sharpen={sharpen}: " + ", ".join(f"{k} {v:.2e}" for k, v in worst.items()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_replay_gpu_with_the_default_page_size(tmp_path, name, dtype):
+    """The same traces with pages as large as the engine makes them when nobody says otherwise (the tests above
+    use small pages, which put more page edges into a sequence)."""
+    from llmengine_b200.config import EngineConfig
+    _run_all(tmp_path, name, dtype, 2.0 if dtype == "bfloat16" else 3.0, None, "cuda:0", page_size=EngineConfig().page_size)
 
 
 @pytest.mark.gpu
