@@ -8,8 +8,15 @@
 //   attention_decode_kernel   one new token per request: the query heads of one key/value head
 //                             form the (padded) 16-row tile, the context is split over blocks and
 //                             over the four warps of a block (each warp streams its own 16-key
-//                             sub-tiles), partial (max, sum, output) triples go to scratch memory
-//                             and the block that finishes last for a head merges them.
+//                             sub-tiles).  Up to 8 splits are launched as a thread-block cluster
+//                             and hand their partial (max, sum, output) triples to the cluster's
+//                             first block through distributed shared memory; with more splits the
+//                             triples go to scratch memory and the block that finishes last for a
+//                             head merges them.  Nobody waits for anybody except at the cluster
+//                             barrier, which every block of a cluster reaches.  The kernel can take
+//                             the raw q|k|v projections of the new tokens instead of finished
+//                             queries (FusedQkv): it then applies QK norm and rotation itself and
+//                             stores the new key and value in the cache.
 //
 // Both read keys and values only from the cache pages through the block table, mask by the
 // absolute position of each query (causal, optional window) and never let a cache row outside
@@ -375,8 +382,8 @@ __global__ void __launch_bounds__(THREADS, PORTION_BLOCKS_PER_SM) attention_port
 // 16-key sub-tiles w, w+4, w+8, ... of the block's share and streams them through a pipeline of its own
 // (DSTAGES sub-tiles in flight per warp, no block-wide barrier inside the loop), so that enough bytes are
 // in flight to cover the memory latency.  At the end the warps' partial results are merged in shared
-// memory; with more than one split the block's result goes to scratch memory and the last block to
-// arrive merges the splits.
+// memory; with more than one split the block's result goes to the first block of its cluster (up to 8
+// splits) or to scratch memory, where the last block to arrive merges the splits.
 // Scratch per (request row, query head, split): HD outputs (not normalised), then max (base-2 units) and sum.
 constexpr int PART = HD + 2;
 // Scratch layout: COUNTER_WORDS ticket counters (one per (request, key/value head) of a call; they must be
