@@ -110,7 +110,7 @@ class ClockSampler:
 
 def reference_arm(args) -> int:
     # The reference is a CMake/C++ project without any Python packaging (no setup.py, no pyproject.toml),
-    # so the offline `pip install --target baseline/_ref /root/reference` has nothing to build; its
+    # so an offline `pip install --target baseline/_ref <the reference's source tree>` has nothing to build; its
     # generate_cuda example also needs a GGUF file with tokenizer metadata and runs one sequence at a
     # time, so the batch-8 metric on random Qwen3-8B weights cannot be produced through its stock path.
     print(json.dumps({"impl": "reference", "unavailable":
