@@ -489,6 +489,18 @@ def test_attention_decode_any_number_of_splits(ops, splits):
     assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("splits", [1, 3])
+def test_attention_decode_long_context_small_pages(ops, splits):
+    """More block-table entries in a block's share than it keeps in shared memory (it then reads them from
+    global memory), and a far key that matters."""
+    nh, nkv, hd, page = 4, 2, 64, 8
+    ctx_lens, q_lens = [9000, 4500], [1, 1]
+    case = _attention_case(nh, nkv, hd, page, ctx_lens, q_lens, 0, torch.bfloat16, 35, spike=(0, 11))
+    out = _run_fast(ops, case, nh, nkv, hd, page, 0, q_lens, splits=splits)
+    assert torch.isfinite(out).all()
+    assert (out.cpu().float() - case["want"]).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("splits", [1, 4, 16])
 @pytest.mark.parametrize("hd,page,norm,rope", [(128, 64, "bf16", True), (64, 16, "f32", True), (128, 16, None, True),
                                                (32, 8, "bf16", False), (128, 128, None, False)])
