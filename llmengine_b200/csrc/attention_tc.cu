@@ -16,16 +16,19 @@
 //               output accumulator, also in tensor memory.  P_t is read from tensor memory (it replaces
 //               the scores it was made from); V is read as an MN-major operand, exactly as it lies in the cache.
 //   warps 2..17 softmax, eight warps per Q tile: two threads per row, 64 keys of the tile each (a warp may
-//               only touch the 32 lanes of tensor memory given by its index modulo 4).  Both find the row's
-//               maximum over all 128 scores by themselves, keep a lazily moved reference maximum and their
-//               half of the sum in 32-bit, and store the probabilities as bfloat16 pairs back into tensor
-//               memory (tcgen05.st) over their own scores, after a 64-thread named barrier with the partner.
+//               only touch the 32 lanes of tensor memory given by its index modulo 4).  Each reads its
+//               scores once, takes the probabilities relative to the row's reference maximum of the tile
+//               before and tells its partner its half's maximum (shared memory, a 64-thread named
+//               barrier); only if the row's maximum has grown by more than 2^8 does the reference move,
+//               the accumulator get rescaled and the scores get read again.  Sums are 32-bit; the
+//               probabilities go back into tensor memory as bfloat16 pairs (tcgen05.st) over the thread's
+//               own scores.
 //
 // Every mbarrier wait is bounded; a wait that gives up sets an error flag (read with
 // llme_attention_tc_status()), and the block drains its copies, frees its tensor memory and returns.  A warp
 // that has given up still attends every named barrier of its pair.
 //
-// Measured (2,048-token prompt, 32 query and 8 key/value heads of 128, B200): 63 us; one Q tile per block with
+// Measured (2,048-token prompt, 32 query and 8 key/value heads of 128, B200): 60 us; one Q tile per block with
 // P in shared memory took 71 us, and was bound by the L2 traffic of every block re-reading the keys and values
 // and by the one thread that issues the matrix instructions (about 0.6 us per group of eight).
 //
@@ -247,6 +250,7 @@ struct Barriers {
     unsigned tmem_base;
     int abort_flag;
     float row_sum[QT][2][BM];     // the two halves' sums of a row, at the end
+    float row_max[QT][2][2][BM];  // [Q tile][tile parity][half][row]: the halves' maxima of a key tile
 };
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -468,14 +472,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     } else {
         // ------------------------------------------------------------------ softmax and output
         // Warp w may touch the 32 lanes of tensor memory given by w % 4 (a quarter of a Q tile's rows); the four
-        // warps with the same quarter serve (Q tile 0 | 1) x (first | second half of the columns).  Both threads
-        // of a row find the row's maximum over all 128 scores of the tile by themselves (the same loads, the
-        // same arithmetic, the same result: nothing to exchange), then each turns its 64 scores into
-        // probabilities.  The output accumulator stays in tensor memory and is added to by the matrix warp
-        // tile after tile.  A row's probabilities are taken relative to a reference maximum that is only moved
-        // when the true maximum has grown by more than RESCALE (in base-2 units): the final division by the
-        // sum, taken relative to the same reference, makes the result exact, and moving the reference means a
-        // round trip of the accumulator through registers, which then happens only in the first few tiles.
+        // warps with the same quarter serve (Q tile 0 | 1) x (first | second half of the columns).  The output
+        // accumulator stays in tensor memory and is added to by the matrix warp tile after tile.  A row's
+        // probabilities are taken relative to a reference maximum that is only moved when the true maximum has
+        // grown by more than RESCALE (in base-2 units): the final division by the sum, taken relative to the
+        // same reference, makes the result exact, and moving the reference means a round trip of the accumulator
+        // through registers and a second reading of the scores, which then happens only in the first few tiles.
         constexpr float RESCALE = 8.0f;
         constexpr int BH = BN / 2;                           // keys of a tile per thread
         constexpr int OC = HD / 2;                           // columns of the output accumulator per thread
@@ -501,89 +503,97 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + t * 4 + quarter) : "memory"); };
             float m_ref = -INFINITY, l_run = 0.0f;
             bool ok = true;
-            // (every iteration comes to the pair's named barrier exactly once, also after a wait has given up: the
-            // partner must never be left waiting there)
             for (int i = 0; i < n_tiles; ++i) {
                 const int j0 = (tile_first + i) * BN;
                 unsigned pk[32];
+                const int s2 = i & 1;
                 ok = ok && mbar_wait(&bar->s_full[t], i & 1, abort_flag, 30);
+                bool unmasked = false;
+                float own_max = -INFINITY;
+                const float ref_old = m_ref == -INFINITY ? 0.0f : m_ref;
+                float sum = 0.0f;
+                // This thread's 64 scores -> probabilities, their sum and their maximum.  The probabilities are taken
+                // relative to the reference maximum of the tile before: it almost never has to move (only when the
+                // row's maximum has grown by more than RESCALE), and then the scores are read a second time below.
+                auto half_pass = [&](float ref, bool with_max) {
+                    float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};          // four partial sums, added in a fixed order
+                    float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int c0 = 0; c0 < BH; c0 += 32) {
+                        float v[32];
+                        tmem_ld32(tmem_s[t] + lane_off + (unsigned)(ch * BH + c0), v);
+                        if (!unmasked) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                const int j = j0 + ch * BH + c0 + e;
+                                if (j < plo || j > phi) v[e] = -INFINITY;
+                            }
+                        }
+                        if (with_max) {
+#pragma unroll
+                            for (int e = 0; e < 32; e += 4) {
+                                mq[0] = fmaxf(mq[0], v[e]); mq[1] = fmaxf(mq[1], v[e + 1]);
+                                mq[2] = fmaxf(mq[2], v[e + 2]); mq[3] = fmaxf(mq[3], v[e + 3]);
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 32; e += 2) {
+                            const float e0 = fast_exp2(fmaf(v[e], sc, -ref));            // a masked score is -inf: exactly 0
+                            const float e1 = fast_exp2(fmaf(v[e + 1], sc, -ref));
+                            sq[(e >> 1) & 3] += e0 + e1;
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
+                            pk[(c0 + e) >> 1] = *reinterpret_cast<unsigned*>(&hh);
+                        }
+                    }
+                    sum = (sq[0] + sq[1]) + (sq[2] + sq[3]);
+                    if (with_max) own_max = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+                };
                 if (ok) {
-                if (warp == 2 && lane == 0) trace(4, i);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const bool unmasked = warp_full && j0 + BN - 1 <= warp_p_lo && j0 >= warp_lo_last;
-                // the row's maximum over the whole tile
-                float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int c = 0; c < BN; c += 32) {
-                    float v[32];
-                    tmem_ld32(tmem_s[t] + lane_off + (unsigned)c, v);
-                    if (!unmasked) {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const int j = j0 + c + e;
-                            if (j < plo || j > phi) v[e] = -INFINITY;
-                        }
-                    }
-#pragma unroll
-                    for (int e = 0; e < 32; e += 4) {
-                        mq[0] = fmaxf(mq[0], v[e]); mq[1] = fmaxf(mq[1], v[e + 1]);
-                        mq[2] = fmaxf(mq[2], v[e + 2]); mq[3] = fmaxf(mq[3], v[e + 3]);
-                    }
+                    if (warp == 2 && lane == 0) trace(4, i);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    unmasked = warp_full && j0 + BN - 1 <= warp_p_lo && j0 >= warp_lo_last;
+                    half_pass(ref_old, true);
                 }
-                const float m_true = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])) * sc;
-                const bool move = m_true > m_ref + RESCALE || (m_ref == -INFINITY && m_true > -INFINITY);
-                const float m_new = move ? m_true : m_ref;
-                const float ref = m_new == -INFINITY ? 0.0f : m_new;
-                if (i > 0 && __any_sync(0xffffffffu, move)) {
-                    // The accumulator is at rest once P V of the tile before has finished.  Both threads of a row
-                    // take the same decision; each rescales its half of the accumulator's columns.
-                    ok = mbar_wait(&bar->p_empty[t], (i & 1) ^ 1, abort_flag, 31);
-                    if (ok) {
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const float corr = move ? fast_exp2(m_ref - ref) : 1.0f;
-                        l_run *= corr;
-#pragma unroll 1
-                        for (int c = 0; c < OC; c += 32) {
-                            float v[32];
-                            tmem_ld32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) v[e] *= corr;
-                            tmem_st32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
-                        }
-                    }
-                } else if (move) {
-                    l_run *= fast_exp2(m_ref - ref);                 // first tile: nothing accumulated yet
-                }
-                m_ref = m_new;
-                // Probabilities of this thread's 64 keys, their sum, and the bfloat16 P values, two per 32-bit word:
-                // 32 words that replace the first 32 of the thread's own 64 scores in tensor memory (the matrix
-                // warp reads them from there as its A operand).
-                float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};              // four partial sums, added in a fixed order below
-#pragma unroll
-                for (int c0 = 0; c0 < BH; c0 += 32) {
-                    float v[32];
-                    tmem_ld32(tmem_s[t] + lane_off + (unsigned)(ch * BH + c0), v);
-                    if (!unmasked) {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const int j = j0 + ch * BH + c0 + e;
-                            if (j < plo || j > phi) v[e] = -INFINITY;
-                        }
-                    }
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const float e0 = fast_exp2(fmaf(v[e], sc, -ref));            // a masked score is -inf: exactly 0
-                        const float e1 = fast_exp2(fmaf(v[e + 1], sc, -ref));
-                        sq[(e >> 1) & 3] += e0 + e1;
-                        __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
-                        pk[(c0 + e) >> 1] = *reinterpret_cast<unsigned*>(&hh);
-                    }
-                }
-                l_run += (sq[0] + sq[1]) + (sq[2] + sq[3]);
-                }
-                // the partner has finished its pass over all of the row's scores (it read this thread's half too)
+                // the two threads of a row tell each other their half's maximum (every iteration comes to the pair's
+                // named barrier exactly once, also after a wait has given up: the partner must never be left there)
+                bar->row_max[t][s2][ch][row] = own_max;
                 pair_sync();
                 if (ok) {
+                    const float m_true = fmaxf(own_max, bar->row_max[t][s2][ch ^ 1][row]) * sc;
+                    const bool move = m_true > m_ref + RESCALE || (m_ref == -INFINITY && m_true > -INFINITY);
+                    if (__any_sync(0xffffffffu, move)) {
+                        // The reference maximum of some row of this warp moves.  Both threads of a row take the same
+                        // decision; each rescales its half of the accumulator's columns (at rest once P V of the tile
+                        // before has finished) and takes its probabilities again, relative to the new reference.
+                        const float m_new = move ? m_true : m_ref;
+                        const float ref = m_new == -INFINITY ? 0.0f : m_new;
+                        if (i > 0) {
+                            ok = mbar_wait(&bar->p_empty[t], (i & 1) ^ 1, abort_flag, 31);
+                            if (ok) {
+                                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                                const float corr = move ? fast_exp2(m_ref - ref) : 1.0f;
+                                l_run *= corr;
+#pragma unroll 1
+                                for (int c = 0; c < OC; c += 32) {
+                                    float v[32];
+                                    tmem_ld32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
+#pragma unroll
+                                    for (int e = 0; e < 32; ++e) v[e] *= corr;
+                                    tmem_st32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
+                                }
+                            }
+                        } else if (move) {
+                            l_run *= fast_exp2(m_ref - ref);         // first tile: nothing accumulated yet (and l_run is 0)
+                        }
+                        m_ref = m_new;
+                        if (ok) half_pass(ref, false);
+                    }
+                }
+                if (ok) {
+                    l_run += sum;
+                    // the probabilities replace the first 32 of this thread's own 64 scores in tensor memory, two
+                    // bfloat16 values per word (the matrix warp reads them from there as its A operand); nobody
+                    // else reads these columns
                     tmem_st32u(tmem_s[t] + lane_off + (unsigned)(ch * BH), pk);
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
