@@ -215,7 +215,7 @@ def breakdown(args) -> int:
         ]
         if ops.linear_swiglu_supports(h, blocks[0].ffn.w_gate_up, act):
             table.append(("gate|up product + swiglu", lambda l: ops.linear_swiglu(h, blocks[l].ffn.w_gate_up, act), 2 * I * H))
-        else:                                  # between 17 and 127 tokens: the library product, then the activation
+        else:                                  # where no fused kernel is taken: the library product, then the activation
             gu = torch.empty(rows, 2 * I, device="cuda", dtype=torch.bfloat16)
             table.append(("gate|up product", lambda l: ops.linear(h, blocks[l].ffn.w_gate_up, gu), 2 * I * H))
             table.append(("swiglu", lambda l: ops.swiglu(gu, act), 0))

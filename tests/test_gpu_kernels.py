@@ -237,9 +237,10 @@ def test_tcgen05_gemm_more_tiles_than_sms(ops, M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("M,inter,K", [(2048, 12288, 4096), (128, 128, 64), (300, 1000, 264), (129, 72, 520), (1000, 136, 8)])
-def test_tcgen05_gemm_with_swiglu(ops, M, inter, K):
+def test_tcgen05_gemm_with_swiglu(ops, monkeypatch, M, inter, K):
     """The tcgen05 product with the activation in its epilogue against the product followed by the activation
     kernel, and against 64-bit arithmetic; widths that end inside a tile."""
+    monkeypatch.setattr(ops, "plain_gemm", "tcgen05")     # also at sizes that the product path gives to cuBLAS
     a = _rand(M, K, dtype=torch.bfloat16, seed=48)
     w = _rand(2 * inter, K, dtype=torch.bfloat16, seed=49, scale=0.08)
     fused = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
