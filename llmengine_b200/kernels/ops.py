@@ -29,6 +29,7 @@ class KernelError(RuntimeError):
 
 
 _F32, _BF16 = 0, 1
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
 def _code(dt: torch.dtype) -> int:
@@ -106,6 +107,7 @@ class CudaOps:
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise KernelsUnavailable(f"device {device} is not a CUDA device")
+        self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._libs: Dict[str, ctypes.CDLL] = {}
         self.use_tcgen05 = True    # products of 128 tokens or more on this package's tcgen05 kernel, else cuBLAS
         self.plain_gemm = os.environ.get("LLME_GEMM", "auto")   # "auto" | "tcgen05" | "cublas", see _tc_fills_its_waves
@@ -145,8 +147,10 @@ class CudaOps:
             msg = lib.llme_last_error().decode("utf-8", "replace")
             raise KernelError(f"{what}: {msg} (code {rc})")
 
-    @staticmethod
-    def _stream() -> c_void_p:
+    def _stream(self) -> c_void_p:
+        # the current stream's handle; the raw getter costs a fraction of a microsecond, the Stream object ten
+        if _raw_stream is not None:
+            return c_void_p(_raw_stream(self._device_index))
         return c_void_p(torch.cuda.current_stream().cuda_stream)
 
     # ------------------------------------------------------------------ kernels

@@ -95,6 +95,7 @@ class Runtime:
         self.max_tokens = max_tokens
         self.kernels = kernels
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[Tuple[str, torch.dtype, int, int], torch.Tensor] = {}   # the views handed out, by shape
         self._tables: Dict[Any, torch.Tensor] = {}
 
     def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype, exact: bool = False,
@@ -103,10 +104,14 @@ class Runtime:
         step (so captured steps can be replayed), grown only when a larger shape is asked for.
         `exact`: the buffer is not indexed by tokens, make it only as large as asked for.
         `zero`: the memory is zeroed when it is allocated (not at later calls)."""
+        view = self._views.get((name, dtype, rows, cols))
+        if view is not None:
+            return view
         key = (name, dtype)
         need = max(rows, 1) * cols
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < need:
+            self._views = {k: v for k, v in self._views.items() if k[:2] != key}   # they show the old memory
             full = self.max_tokens * cols
             itemsize = torch.empty((), dtype=dtype).element_size()
             # token-indexed buffers are made for the step's token budget at once; very wide ones
@@ -114,7 +119,10 @@ class Runtime:
             cap = max(need, full) if (not exact and full * itemsize <= (256 << 20)) else need
             buf = (torch.zeros if zero else torch.empty)(cap, dtype=dtype, device=self.device)
             self._buffers[key] = buf
-        return buf[: rows * cols].view(rows, cols)
+        view = buf[: rows * cols].view(rows, cols)
+        if len(self._views) < 4096:
+            self._views[(name, dtype, rows, cols)] = view
+        return view
 
     def shared_table(self, key: Any, make: Callable[[], torch.Tensor]) -> torch.Tensor:
         """Constant tables (rotary cos/sin) built once per distinct key and shared by all layers."""
