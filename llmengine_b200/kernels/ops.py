@@ -359,7 +359,15 @@ class CudaOps:
             # many tokens: this package's tcgen05 kernel (TMA-fed, accumulator in tensor memory)
             return self.linear_tc(x, w, out)
         if out.dtype == torch.bfloat16:
-            torch.mm(x, w.t(), out=out)
+            # torch lets cuBLAS add partial sums in bfloat16 unless told otherwise, and for some shapes (a few
+            # tokens, an odd width) cuBLAS then does: results a thousand rounding steps off.  Not here.
+            mm = torch.backends.cuda.matmul
+            keep = mm.allow_bf16_reduced_precision_reduction
+            mm.allow_bf16_reduced_precision_reduction = False
+            try:
+                torch.mm(x, w.t(), out=out)
+            finally:
+                mm.allow_bf16_reduced_precision_reduction = keep
         else:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         return out

@@ -125,6 +125,25 @@ def test_linear_bf16(ops, M, N, K):
     assert (out16.cpu().float() - want).abs().max() < 0.02 * want.abs().max()
 
 
+@pytest.mark.parametrize("M,N,K", [(7, 576, 161), (12, 543, 119), (16, 543, 160), (17, 543, 4096), (64, 543, 4100),
+                                   (33, 80, 4100), (5, 1131, 119)])
+def test_linear_bf16_sums_in_32bit_whatever_the_shape(ops, M, N, K):
+    """Products that go to the library (a width that is no multiple of 8, or 17 to 127 tokens): every output is
+    within a few bfloat16 steps of the exact value, also where the library, left to itself, adds partial sums
+    in bfloat16 (a few tokens and odd sizes: a thousand steps off)."""
+    a = _rand(M, K, dtype=torch.bfloat16, seed=15)
+    w = _rand(N, K, dtype=torch.bfloat16, seed=16, scale=0.1)
+    want = (a.double() @ w.double().t()).cpu()
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear(a, w, out16)
+    # 32-bit accumulation of K products of size |a||w|, then one rounding to bfloat16
+    sums = (a.double().abs() @ w.double().abs().t()).cpu()
+    assert ((out16.double().cpu() - want).abs() <= want.abs() * 2 ** -8 + sums * 2e-6).all()
+    out32 = torch.empty(M, N, device=DEV)
+    ops.linear(a, w, out32)
+    assert ((out32.double().cpu() - want).abs() <= sums * 2e-6).all()
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 72), (129, 257, 264), (300, 1000, 96), (2048, 520, 1024),
                                    (1000, 4096, 4096), (257, 24, 8)])

@@ -16,7 +16,7 @@ import torch
 from helpers import (compare, engine_for, make_model_dir, max_live_tokens, random_ids, replay, trace_bulk_then_single,
                      trace_mixed, trace_portions, trace_whole)
 from plain_model import PlainQwen3
-from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
+from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D, TINY_E
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -43,6 +43,7 @@ CONFIGS = {
     "B": (TINY_B, 8, [1, 5, 64, 130, 200, 48]),
     "C": (TINY_C, 16, [90, 37, 120, 64, 23]),
     "D": (TINY_D, 16, [300, 129, 40, 520, 128, 17]),
+    "E": (TINY_E, 32, [2, 128, 200, 33, 127]),
 }
 
 
@@ -93,7 +94,7 @@ def test_host_logic_replay_cpu(tmp_path, name):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,sharpen", [("float32", 1.0), ("float32", 3.0), ("bfloat16", 1.0), ("bfloat16", 2.0)])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_replay_gpu(tmp_path, name, dtype, sharpen):
     """`sharpen` scales the QK-norm gains: attention becomes peaked, so that a key that is skipped,
     read from a wrong page or seen through a wrong mask moves the logits by far more than the tolerance."""

@@ -32,3 +32,11 @@ TINY_D = {
     "vocab_size": 600, "rope_theta": 300000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": False,
     "max_position_embeddings": 640, "hidden_act": "silu",
 }
+
+# E: odd sizes everywhere (no vector loads, products that only the library takes), one query head per key head
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 119,
+    "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 80, "intermediate_size": 99,
+    "vocab_size": 1131, "rope_theta": 777.0, "rms_norm_eps": 3e-4, "tie_word_embeddings": True,
+    "max_position_embeddings": 320, "hidden_act": "silu",
+}
