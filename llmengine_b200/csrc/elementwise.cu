@@ -6,6 +6,8 @@
 // :380-397, rmsnorm_kernel :360-378 (also used as QK norm), add_kernel :224-227,
 // rope_kernel :430-450, swiglu_kernel :245-248, and the per-token cudaMemcpy cache
 // writes of src/runtime/cache/paged_kv_cache.cpp:189-207, which the fused write replaces.
+#include <type_traits>
+
 #include "common.cuh"
 
 LLME_API const char* llme_last_error() { return llme_error_buffer(); }
@@ -485,6 +487,176 @@ __global__ void qkv_post_vec_kernel(QkvArgs a) {
     }
 }
 
+// Many tokens, bfloat16 in and out, a head size of 32, 64, 128 or 256: a warp takes one token and a run of
+// heads.  What belongs to the token (its position's cos/sin values, its cache slot, the gains) is loaded once
+// per warp instead of once per head, a lane holds 4 + 4 values of a head (8-byte loads and stores), and the
+// 32 lanes cover 32 / LPH heads at a time, so that a head costs about half the instructions of the kernel above.
+constexpr int QKV_WIDE_ITERS = 2;      // head groups per warp
+constexpr int QKV_WIDE_WARPS = 8;      // = tokens per block
+
+__device__ __forceinline__ void bf16x4_to_f32(uint2 v, float (&f)[4]) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ uint2 f32_to_bf16x4(const float (&f)[4]) {
+    uint2 v;
+    *reinterpret_cast<__nv_bfloat162*>(&v.x) = __floats2bfloat162_rn(f[0], f[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&v.y) = __floats2bfloat162_rn(f[2], f[3]);
+    return v;
+}
+template <typename G> __device__ __forceinline__ void load_gain4(const G* p, float (&g)[4]);
+template <> __device__ __forceinline__ void load_gain4<float>(const float* p, float (&g)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    g[0] = v.x; g[1] = v.y; g[2] = v.z; g[3] = v.w;
+}
+template <> __device__ __forceinline__ void load_gain4<__nv_bfloat16>(const __nv_bfloat16* p, float (&g)[4]) {
+    bf16x4_to_f32(*reinterpret_cast<const uint2*>(p), g);
+}
+
+template <typename G, int LPH>
+__global__ void __launch_bounds__(QKV_WIDE_WARPS * 32, 4) qkv_post_wide_kernel(QkvArgs a) {
+    pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
+    pdl_wait();                // everything below reads or writes what earlier kernels touch
+    typedef __nv_bfloat16 bf16;
+    constexpr int HPW = 32 / LPH;                  // heads the warp's lanes cover at a time
+    constexpr int HD = LPH * 8, HALF = HD / 2;
+    const int lane = threadIdx.x & 31;
+    const int t = (int)blockIdx.x * QKV_WIDE_WARPS + (int)(threadIdx.x >> 5);
+    if (t >= a.tokens) return;
+    const int heads = a.nh + 2 * a.nkv;
+    const int d = 4 * (lane % LPH);                // this lane's values: d .. d+3 and HALF+d .. HALF+d+3
+    const int h0 = (int)blockIdx.y * (HPW * QKV_WIDE_ITERS) + lane / LPH;
+
+    // the heads first (the loads that take longest), then what belongs to the token
+    uint2 lo[QKV_WIDE_ITERS], hi[QKV_WIDE_ITERS];
+#pragma unroll
+    for (int it = 0; it < QKV_WIDE_ITERS; ++it) {
+        const int h = h0 + it * HPW;
+        const bf16* src = nullptr;
+        if (h < a.nh) { if (a.q_in) src = (const bf16*)a.q_in + (size_t)t * a.q_stride + (size_t)h * HD; }
+        else if (h < a.nh + a.nkv) { if (a.k_in) src = (const bf16*)a.k_in + (size_t)t * a.k_stride + (size_t)(h - a.nh) * HD; }
+        else if (h < heads) { if (a.v_in) src = (const bf16*)a.v_in + (size_t)t * a.v_stride + (size_t)(h - a.nh - a.nkv) * HD; }
+        lo[it] = make_uint2(0u, 0u); hi[it] = make_uint2(0u, 0u);
+        if (src) {
+            lo[it] = *reinterpret_cast<const uint2*>(src + d);
+            hi[it] = *reinterpret_cast<const uint2*>(src + HALF + d);
+        }
+    }
+    float co[4] = {1.0f, 1.0f, 1.0f, 1.0f}, si[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (a.cos_sin) {
+        int pos = a.positions[t];
+        pos = pos < 0 ? 0 : (pos >= a.max_positions ? a.max_positions - 1 : pos);   // the host refuses such positions
+        const float* cs = a.cos_sin + (size_t)pos * HD;
+        load_gain4<float>(cs + d, co);
+        load_gain4<float>(cs + HALF + d, si);
+    }
+    float qg0[4], qg1[4], kg0[4], kg1[4];
+    if (a.q_gain) { load_gain4<G>((const G*)a.q_gain + d, qg0); load_gain4<G>((const G*)a.q_gain + HALF + d, qg1); }
+    if (a.k_gain) { load_gain4<G>((const G*)a.k_gain + d, kg0); load_gain4<G>((const G*)a.k_gain + HALF + d, kg1); }
+    bf16* cache_row = nullptr;                     // the token's place in the cache: key of head 0
+    size_t kv_step = 0, head_step = 0;
+    if (a.cache) {
+        const int slot = a.slot_mapping[t];
+        if (slot >= 0) {
+            const int page = slot / a.page_size, off = slot - page * a.page_size;
+            head_step = (size_t)a.page_size * HD;
+            kv_step = (size_t)a.nkv * head_step;
+            cache_row = (bf16*)a.cache + (size_t)page * 2 * kv_step + (size_t)off * HD;
+        }
+    }
+
+#pragma unroll
+    for (int it = 0; it < QKV_WIDE_ITERS; ++it) {
+        const int h = h0 + it * HPW;
+        const bool is_q = h < a.nh, is_k = !is_q && h < a.nh + a.nkv, is_v = !is_q && !is_k && h < heads;
+        float x0[4], x1[4];
+        bf16x4_to_f32(lo[it], x0);
+        bf16x4_to_f32(hi[it], x1);
+        // every lane takes part in the sums, whatever its head is
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ss += x0[i] * x0[i] + x1[i] * x1[i];
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (is_v) {
+            if (cache_row && a.v_in) {
+                bf16* dst = cache_row + kv_step + (size_t)(h - a.nh - a.nkv) * head_step;
+                *reinterpret_cast<uint2*>(dst + d) = lo[it];
+                *reinterpret_cast<uint2*>(dst + HALF + d) = hi[it];
+            }
+            continue;
+        }
+        if (!(is_q || is_k) || !(is_q ? a.q_in : a.k_in)) continue;
+        if (is_q ? a.q_gain != nullptr : a.k_gain != nullptr) {
+            const float rinv = 1.0f / sqrtf(ss / (float)HD + a.eps);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                x0[i] = (x0[i] * rinv) * (is_q ? qg0[i] : kg0[i]);
+                x1[i] = (x1[i] * rinv) * (is_q ? qg1[i] : kg1[i]);
+            }
+        }
+        if (a.cos_sin) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float u = x0[i], v = x1[i];
+                x0[i] = u * co[i] - v * si[i];
+                x1[i] = u * si[i] + v * co[i];
+            }
+        }
+        const uint2 o0 = f32_to_bf16x4(x0), o1 = f32_to_bf16x4(x1);
+        if (is_q) {
+            if (a.q_out) {
+                bf16* dst = (bf16*)a.q_out + ((size_t)t * a.nh + h) * HD;
+                *reinterpret_cast<uint2*>(dst + d) = o0;
+                *reinterpret_cast<uint2*>(dst + HALF + d) = o1;
+            }
+        } else {
+            const int head = h - a.nh;
+            if (a.k_out) {
+                bf16* dst = (bf16*)a.k_out + ((size_t)t * a.nkv + head) * HD;
+                *reinterpret_cast<uint2*>(dst + d) = o0;
+                *reinterpret_cast<uint2*>(dst + HALF + d) = o1;
+            }
+            if (cache_row) {
+                bf16* dst = cache_row + (size_t)head * head_step;
+                *reinterpret_cast<uint2*>(dst + d) = o0;
+                *reinterpret_cast<uint2*>(dst + HALF + d) = o1;
+            }
+        }
+    }
+}
+
+template <typename G, int LPH>
+static void launch_qkv_wide_lph(const QkvArgs& a, cudaStream_t s) {
+    const int heads = a.nh + 2 * a.nkv;
+    const int per_warp = (32 / LPH) * QKV_WIDE_ITERS;
+    llme_launch(qkv_post_wide_kernel<G, LPH>, dim3((unsigned)((a.tokens + QKV_WIDE_WARPS - 1) / QKV_WIDE_WARPS), (unsigned)((heads + per_warp - 1) / per_warp)),
+                dim3(QKV_WIDE_WARPS * 32), 0, s, a);
+}
+
+// Whether the wide kernel takes this call (and then launches it): bfloat16 in and out is the caller's business.
+template <typename G>
+static bool launch_qkv_wide(const QkvArgs& a, cudaStream_t s) {
+    const int heads = a.nh + 2 * a.nkv;
+    if (a.hd != 32 && a.hd != 64 && a.hd != 128 && a.hd != 256) return false;
+    const int groups = (heads + (256 / a.hd) * QKV_WIDE_ITERS - 1) / ((256 / a.hd) * QKV_WIDE_ITERS);
+    if (groups > 65535) return false;
+    if ((long long)a.tokens * groups < 148LL * 16) return false;                // few tokens: a warp per (token, head)
+    if ((a.q_stride | a.k_stride | a.v_stride) & 3) return false;
+    const uintptr_t ptrs = (uintptr_t)a.q_in | (uintptr_t)a.k_in | (uintptr_t)a.v_in | (uintptr_t)a.q_gain |
+                           (uintptr_t)a.k_gain | (uintptr_t)a.cos_sin | (uintptr_t)a.q_out | (uintptr_t)a.k_out |
+                           (uintptr_t)a.cache;
+    if (ptrs % 16) return false;
+    switch (a.hd) {
+        case 32: launch_qkv_wide_lph<G, 4>(a, s); break;
+        case 64: launch_qkv_wide_lph<G, 8>(a, s); break;
+        case 128: launch_qkv_wide_lph<G, 16>(a, s); break;
+        default: launch_qkv_wide_lph<G, 32>(a, s); break;
+    }
+    return true;
+}
+
 constexpr int QKV_WARPS_PER_BLOCK = 8;
 constexpr int QKV_TOKENS_PER_WARP = 4;
 
@@ -523,9 +695,12 @@ static int dispatch_qkv_gain(const QkvArgs& a, cudaStream_t s) {
     const int wpb = 8;
     const long long blocks = (warps + wpb - 1) / wpb;
     if (blocks > 2147483647LL) LLME_REFUSE("qkv_post: too many (token, head) pairs for one launch");
+    constexpr bool BF16_IO = std::is_same<I, __nv_bfloat16>::value && std::is_same<O, __nv_bfloat16>::value;
     if (a.gain_dtype == LLME_F32 || !(a.q_gain || a.k_gain)) {
+        if (BF16_IO && launch_qkv_wide<float>(a, s)) LLME_LAUNCH_STATUS();
         if (launch_qkv_vec<I, O, float>(a, s)) LLME_LAUNCH_STATUS();
     } else if (a.gain_dtype == LLME_BF16) {
+        if (BF16_IO && launch_qkv_wide<__nv_bfloat16>(a, s)) LLME_LAUNCH_STATUS();
         if (launch_qkv_vec<I, O, __nv_bfloat16>(a, s)) LLME_LAUNCH_STATUS();
     }
     if (a.gain_dtype == LLME_F32) llme_launch(qkv_post_kernel<I, O, float>, dim3((unsigned)blocks), dim3(wpb * 32), 0, s, a);

@@ -294,15 +294,30 @@ def _paged_layout(T, page_size, num_pages, seed):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 8), (6, 3, 48, 16), (8, 1, 80, 4), (32, 8, 128, 16), (2, 2, 256, 32)])
 def test_qkv_post(ops, dtype, nh, nkv, hd, page):
+    _check_qkv_post(ops, dtype, nh, nkv, hd, page, 29, torch.float32)
+
+
+@pytest.mark.parametrize("dtype,gain_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32),
+                                              (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("nh,nkv,hd,page,T", [(32, 8, 128, 64, 1001), (5, 1, 64, 16, 3000), (3, 3, 32, 8, 2500),
+                                              (2, 1, 256, 32, 4003), (6, 3, 48, 16, 4500), (7, 7, 128, 128, 700)])
+def test_qkv_post_many_tokens(ops, dtype, gain_dtype, nh, nkv, hd, page, T):
+    """The kernels that a prompt portion takes (a warp per token and run of heads for bfloat16 with a head size
+    of 32, 64, 128 or 256, else a warp per head of four tokens): head counts that end inside a warp's run,
+    token counts that end inside a block."""
+    _check_qkv_post(ops, dtype, nh, nkv, hd, page, T, gain_dtype)
+
+
+def _check_qkv_post(ops, dtype, nh, nkv, hd, page, T, gain_dtype):
     from llmengine_b200.parts.position import RotaryEncoding
-    T, eps, theta, maxpos = 29, 2e-6, 12345.0, 300
+    eps, theta, maxpos = 2e-6, 12345.0, T + 300
     qs, kvs = nh * hd, nkv * hd
     qkv = _rand(T, qs + 2 * kvs, dtype=dtype, seed=15)
-    qg = (1 + 0.1 * _rand(hd, seed=16))
-    kg = (1 + 0.1 * _rand(hd, seed=17))
+    qg = (1 + 0.1 * _rand(hd, seed=16)).to(gain_dtype)
+    kg = (1 + 0.1 * _rand(hd, seed=17)).to(gain_dtype)
     table = RotaryEncoding.build_table(hd, theta, maxpos).to(DEV)
     positions = (torch.arange(T) + 200).to(torch.int32).to(DEV)
-    num_pages = 12
+    num_pages = -(-T // page) + 11
     blocks, slots = _paged_layout(T, page, num_pages, 18)
     slots[5] = -1                                     # a token that is not stored
     cache = torch.zeros(num_pages, 2, nkv, page, hd, dtype=dtype, device=DEV)
@@ -312,22 +327,19 @@ def test_qkv_post(ops, dtype, nh, nkv, hd, page):
                  cache=cache, slot_mapping=slots.to(DEV), page_size=page)
     f = qkv.cpu().float()
     pos = positions.cpu()
-    q_want = pm.rope(pm.qk_norm(f[:, :qs].view(T, nh, hd), qg.cpu(), eps), pos, theta).reshape(T, qs)
-    k_want = pm.rope(pm.qk_norm(f[:, qs:qs + kvs].view(T, nkv, hd), kg.cpu(), eps), pos, theta)
+    q_want = pm.rope(pm.qk_norm(f[:, :qs].view(T, nh, hd), qg.cpu().float(), eps), pos, theta).reshape(T, qs)
+    k_want = pm.rope(pm.qk_norm(f[:, qs:qs + kvs].view(T, nkv, hd), kg.cpu().float(), eps), pos, theta)
     v_want = f[:, qs + kvs:].view(T, nkv, hd)
     tol = 2e-5 if dtype == torch.float32 else 0.04
     assert (q_out.cpu().float() - q_want).abs().max() < tol
-    c = cache.cpu().float()
-    for t in range(T):
-        s = int(slots[t])
-        if s < 0:
-            continue
-        assert (c[s // page, 0, :, s % page] - k_want[t]).abs().max() < tol
-        assert (c[s // page, 1, :, s % page] - v_want[t]).abs().max() < tol
-    written = {int(s) for s in slots if s >= 0}
-    for s in range(num_pages * page):
-        if s not in written:
-            assert c[s // page, :, :, s % page].abs().max() == 0, "a cache row that no token maps to was written"
+    c = cache.cpu().float().permute(0, 3, 1, 2, 4).reshape(num_pages * page, 2, nkv, hd)     # [slot, k|v, head, hd]
+    stored = slots >= 0
+    idx = slots[stored].long()
+    assert (c[idx, 0] - k_want[stored]).abs().max() < tol
+    assert torch.equal(c[idx, 1], v_want[stored])
+    untouched = torch.ones(num_pages * page, dtype=torch.bool)
+    untouched[idx] = False
+    assert c[untouched].abs().max() == 0, "a cache row that no token maps to was written"
 
 
 # ----------------------------------------------------------------------------- attention
