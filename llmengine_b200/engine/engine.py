@@ -43,6 +43,8 @@ class StepEntry:
 
 
 class Engine:
+    SHORT_CONTEXT = 8192        # captured decode steps come in two kinds: every context up to here, and longer ones
+
     def __init__(self, model_dir: Optional[str] = None, *, config=None, random_seed: Optional[int] = None,
                  engine_config: Optional[EngineConfig] = None, ops=None):
         """`model_dir`: a folder with config.json and model.safetensors.  Or `config` (a typed
@@ -93,7 +95,7 @@ class Engine:
         # decode-only steps are captured in CUDA graphs, one per batch size, after one eager step of that size
         self.graphs_enabled = (bool(ec.use_cuda_graphs) and self.device.type == "cuda"
                                and all(p.capture_safe for p in self.model.parts()))
-        self._graphs: Dict[int, tuple] = {}
+        self._graphs: Dict[tuple, tuple] = {}
         self._graph_seen: set = set()
         self._graph_pool = None
 
@@ -362,15 +364,20 @@ class Engine:
         R = batch.num_requests
         if not (self.graphs_enabled and batch.decode_only and batch.logit_rows.numel() == R):
             return self.model.forward(batch, self._caches)
-        rec = self._graphs.get(R)
+        # launch shapes must serve every context length that replays of the capture will meet: one capture for
+        # contexts up to SHORT_CONTEXT (where few blocks per request, merged inside a cluster, are fastest) and
+        # one for everything up to the longest sequence
+        short = batch.max_ctx_len <= self.SHORT_CONTEXT < self.max_model_len
+        key = (R, short)
+        rec = self._graphs.get(key)
         if rec is not None:
             graph, logits, launches, _keep = rec
             graph.replay()
             self.ops.launches += launches
             return logits
-        batch.assume_ctx = self.max_model_len           # launch shapes must serve any later context length
-        if R not in self._graph_seen:                   # first step of this size: eager, so every buffer exists
-            self._graph_seen.add(R)
+        batch.assume_ctx = self.SHORT_CONTEXT if short else self.max_model_len
+        if key not in self._graph_seen:                 # first step of this kind: eager, so every buffer exists
+            self._graph_seen.add(key)
             return self.model.forward(batch, self._caches)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
@@ -382,7 +389,7 @@ class Engine:
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
         # the captured kernels hold raw pointers into the workspace: keep those buffers alive with the graph
-        self._graphs[R] = (graph, logits, launches, dict(self.rt._buffers))
+        self._graphs[key] = (graph, logits, launches, dict(self.rt._buffers))
         graph.replay()
         self.ops.launches += launches
         return logits

@@ -45,7 +45,12 @@ def test_greedy_generation_through_the_entry_point(tmp_path, cfg, page, chunk, d
     assert llm.engine.ops.launches > 0
 
 
-def test_cuda_graph_decoding_gives_the_same_tokens(tmp_path):
+@pytest.mark.parametrize("short_context", [8192, 48])
+def test_cuda_graph_decoding_gives_the_same_tokens(tmp_path, monkeypatch, short_context):
+    """Captured decode steps against eager ones; with the small limit the requests grow past it while they decode,
+    so that both kinds of capture (short contexts, any context) are made and replayed."""
+    from llmengine_b200.engine.engine import Engine
+    monkeypatch.setattr(Engine, "SHORT_CONTEXT", short_context)
     d = make_model_dir(str(tmp_path / "m"), TINY_B, 8, dtype="bfloat16", sharpen=1.5)
     prompts = [random_ids(n, 1000, i) for i, n in enumerate([9, 40, 3])]
     runs = []
