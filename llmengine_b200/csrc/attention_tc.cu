@@ -15,6 +15,11 @@
 //               the tile's score columns of tensor memory, and O_t += P_t V (128 x HEAD_DIM x 128) into its
 //               output accumulator, also in tensor memory.  P_t is read from tensor memory (it replaces
 //               the scores it was made from); V is read as an MN-major operand, exactly as it lies in the cache.
+//               One round is: wait for V(i) | K(i+1) (one barrier) and for P_t(i), sixteen instructions
+//               (O_t(i), then S_t(i+1)), commits.  The pipe holds very few instructions in advance, and an
+//               access of this thread to a barrier in shared memory takes 100 to 160 cycles while the pipe
+//               reads its operands from there: what the thread does between two instructions is time the pipe
+//               stands idle, so waits and commits are few and lie where products are in flight.
 //   warps 2..17 softmax, eight warps per Q tile: two threads per row, 64 keys of the tile each (a warp may
 //               only touch the 32 lanes of tensor memory given by its index modulo 4).  Each reads its
 //               scores once, takes the probabilities relative to the row's reference maximum of the tile
@@ -28,9 +33,12 @@
 // llme_attention_tc_status()), and the block drains its copies, frees its tensor memory and returns.  A warp
 // that has given up still attends every named barrier of its pair.
 //
-// Measured (2,048-token prompt, 32 query and 8 key/value heads of 128, B200): 60 us; one Q tile per block with
-// P in shared memory took 71 us, and was bound by the L2 traffic of every block re-reading the keys and values
-// and by the one thread that issues the matrix instructions (about 0.6 us per group of eight).
+// Measured (2,048-token prompt, 32 query and 8 key/value heads of 128, B200): 56.5 us (the SM clock is about
+// 1.62 GHz while it runs; a round of sixteen instructions then needs 0.71 us of the pipe, the thread's
+// bookkeeping 0.2 to 0.3 us more, and a tile's softmax about 1 us, of which 0.6 us are its 8,192 exponentials
+// on the two warps a scheduler has of it).  With O_t(i) and S_t(i+1) as separate rounds of eight, each with
+// waits and commits of its own: 62.7 us.  One Q tile per block with P in shared memory took 71 us.  A second
+// issuing warp (one per Q tile) made it slower (66.8 us).
 //
 // Reference counterpart: flash_sdpa_tiled_kernel (src/runtime/kernels/cuda_kernels.cu:558-645): one block per
 // query row, scalar FMA, keys of the same launch only.
@@ -245,8 +253,10 @@ __device__ __forceinline__ void trace(int, int) {}
 #endif
 
 struct Barriers {
-    unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
-    unsigned long long s_full[QT], p_full[QT], p_empty[QT], o_full;
+    // kv_full / kv_empty [i % 2]: the values of key tile i together with the keys of tile i + 1, which the
+    // matrix warp takes in one go; the keys of the first tile have a barrier pair of their own
+    unsigned long long q_full, k0_full, k0_empty, kv_full[2], kv_empty[2];
+    unsigned long long s_full[QT], p_full[QT], o_full;
     unsigned tmem_base;
     int abort_flag;
     float row_sum[QT][2][BM];     // the two halves' sums of a row, at the end
@@ -285,16 +295,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     if (threadIdx.x == 0) {
         mbar_init(&bar->q_full, 1);
+        mbar_init(&bar->k0_full, 1);
+        mbar_init(&bar->k0_empty, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bar->k_full[s], 1);
-            mbar_init(&bar->k_empty[s], 1);
-            mbar_init(&bar->v_full[s], 1);
-            mbar_init(&bar->v_empty[s], 1);
+            mbar_init(&bar->kv_full[s], 2);         // the load of the values and the load of the keys
+            mbar_init(&bar->kv_empty[s], 1);
         }
         for (int t = 0; t < QT; ++t) {
             mbar_init(&bar->s_full[t], 1);
             mbar_init(&bar->p_full[t], 8);          // the eight softmax warps of a Q tile
-            mbar_init(&bar->p_empty[t], 1);
         }
         mbar_init(&bar->o_full, 1);
         bar->abort_flag = 0;
@@ -345,19 +354,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int blk = ps_shift >= 0 ? ja >> ps_shift : ja / ps;
             return (long long)bt[blk] * page_rows + head_rows + (ja - blk * ps);
         };
-        // One load of a tile: its keys (which = 0) or its values (1), into the stage i % 2.
-        auto load_tile = [&](int i, int which, long long my_row) {
+        // One load of a tile: its keys (which = 0) or its values (1), into the stage i % 2; `full` counts its bytes,
+        // `empty` (if any) with `empty_parity` says when the stage may be overwritten.
+        auto load_tile = [&](int i, int which, long long my_row, unsigned long long* full, unsigned long long* empty, unsigned empty_parity) {
             const int j0 = (tile_first + i) * BN;
             const int ja = j0 + (my_box << box_shift), jb = ja + rows_per_box - 1;
             const bool whole = my_row >= 0 && ja >= lo_min && jb <= hi_max;
             const unsigned whole_mask = __ballot_sync(0xffffffffu, whole);                 // one bit per TMA load
             const unsigned part_mask = __ballot_sync(0xffffffffu, my_row >= 0 && !whole && my_half == 0);
             const unsigned tx = (unsigned)__popc(whole_mask) * load_bytes;
-            unsigned long long* empty = which ? &bar->v_empty[i & 1] : &bar->k_empty[i & 1];
-            unsigned long long* full = which ? &bar->v_full[i & 1] : &bar->k_full[i & 1];
             unsigned char* tile = (which ? v_tiles : k_tiles) + (i & 1) * TILE_BYTES;
-            const unsigned use = (unsigned)(i >> 1);                                       // how often the stage was filled before
-            ok = mbar_wait(empty, (use & 1) ^ 1, abort_flag, 10 + which) && !*abort_flag;
+            if (empty) ok = mbar_wait(empty, empty_parity, abort_flag, 10 + which);
+            ok = ok && !*abort_flag;
             if (!ok) return;
             if (lane == 0) trace(8 + which, i);
             // First the boxes that straddle an edge of the visible range: they are copied by hand, visible
@@ -389,14 +397,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (lane == 0) trace(which, i);
             __syncwarp();
         };
-        // The keys run one tile ahead of the values: K(i+1) only waits for the scores of tile i-1, V(i) for the
-        // output products of tile i-2, which come a softmax later.
+        // The keys run one tile ahead of the values: the matrix warp takes V(i) and K(i+1) together (O += P V(i),
+        // then S = Q K(i+1)^T), and gives both stages back together when tile i is done.
         long long row_cur = first_row(0), row_next = first_row(1);
-        load_tile(0, 0, row_cur);
+        load_tile(0, 0, row_cur, &bar->k0_full, nullptr, 0u);
         for (int i = 0; i < n_tiles && ok; ++i) {
             const long long row_after = first_row(i + 2);
-            if (i + 1 < n_tiles) load_tile(i + 1, 0, row_next);
-            if (ok) load_tile(i, 1, row_cur);
+            unsigned long long* full = &bar->kv_full[i & 1];
+            unsigned long long* empty = &bar->kv_empty[i & 1];
+            const unsigned parity = ((unsigned)(i >> 1) & 1u) ^ 1u;          // passes at once while the stages are fresh
+            // K(2) goes where K(0) lay, which no kv_empty speaks for
+            if (i == 1) ok = mbar_wait(&bar->k0_empty, 0, abort_flag, 12);
+            if (i + 1 < n_tiles) {
+                if (ok) load_tile(i + 1, 0, row_next, full, empty, parity);
+            } else if (lane == 0) {
+                mbar_arrive(full);                                           // no keys behind the last tile
+            }
+            if (ok) load_tile(i, 1, row_cur, full, empty, parity);
             row_cur = row_next;
             row_next = row_after;
         }
@@ -428,24 +445,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
 #pragma unroll
             for (int s = 0; s < 2; ++s) dv[s] = desc_mn_major(v_tiles + s * TILE_BYTES);
-            auto issue_s = [&](int t, int i) {
-                const int s = i & 1, round = i >> 1;
-                ok = ok && mbar_wait(&bar->k_full[s], round & 1, abort_flag, 21);
+            auto issue_first = [&](int t) {                           // S_t(0) = Q_t K(0)^T
+                ok = ok && mbar_wait(&bar->k0_full, 0, abort_flag, 21);
                 if (!ok) return;
-                // S_t is free: its last readers finished before they filled P_t(i-1), which O_t(i-1) below waited for
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned d = t == 0 ? tmem_s[0] : tmem_s[1];
-                umma_qk_half<true>(d, t == 0 ? dq[0][0] : dq[QT - 1][0], s == 0 ? dk[0][0] : dk[1][0], id_s);
-                if (HALVES == 2)
-                    umma_qk_half<false>(d, t == 0 ? dq[0][HALVES - 1] : dq[QT - 1][HALVES - 1], s == 0 ? dk[0][HALVES - 1] : dk[1][HALVES - 1], id_s);
-                if (t == n_q - 1) umma_commit(&bar->k_empty[s]);      // both Q tiles have read K(i)
+                umma_qk_half<true>(d, t == 0 ? dq[0][0] : dq[QT - 1][0], dk[0][0], id_s);
+                if (HALVES == 2) umma_qk_half<false>(d, t == 0 ? dq[0][HALVES - 1] : dq[QT - 1][HALVES - 1], dk[0][HALVES - 1], id_s);
+                if (t == n_q - 1) umma_commit(&bar->k0_empty);        // both Q tiles have read K(0)
                 umma_commit(&bar->s_full[t]);
-                trace(2 + t, i);
+                trace(2 + t, 0);
             };
-            auto issue_o = [&](int t, int i) {
+            // O_t(i) += P_t(i) V(i) and, straight behind it, S_t(i+1) = Q_t K(i+1)^T: every wait comes before the
+            // sixteen instructions and every commit after them, so that the thread's own bookkeeping (which the
+            // tensor pipe would otherwise stand idle for: it holds very few instructions in advance) overlaps
+            // with the products it has just issued.
+            auto issue_pair = [&](int t, int i) {
                 const int s = i & 1, round = i >> 1;
+                const bool more = i + 1 < n_tiles;
+                const int s1 = s ^ 1;
+                ok = ok && mbar_wait(&bar->kv_full[s], round & 1, abort_flag, 24);
                 ok = ok && mbar_wait(&bar->p_full[t], i & 1, abort_flag, 23);
-                ok = ok && mbar_wait(&bar->v_full[s], round & 1, abort_flag, 24);
                 if (!ok) return;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned d = t == 0 ? tmem_o[0] : tmem_o[1];
@@ -455,19 +475,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 // columns 0..31 of S_t, those of keys 64..127 in columns 64..95
                 umma_pv_half(d, pa, b0, id_o, i > 0 ? 1u : 0u);
                 umma_pv_half(d, pa + 64u, b0 + 4ull * (2048 >> 4), id_o, 1u);
-                umma_commit(&bar->p_empty[t]);
+                if (more) {
+                    // S_t is free again once the products above have read P_t(i); the pipe runs them in order
+                    umma_qk_half<true>(pa, t == 0 ? dq[0][0] : dq[QT - 1][0], s1 == 0 ? dk[0][0] : dk[1][0], id_s);
+                    if (HALVES == 2)
+                        umma_qk_half<false>(pa, t == 0 ? dq[0][HALVES - 1] : dq[QT - 1][HALVES - 1], s1 == 0 ? dk[0][HALVES - 1] : dk[1][HALVES - 1], id_s);
+                    umma_commit(&bar->s_full[t]);
+                }
                 trace(12 + t, i);
                 if (t == n_q - 1) {
-                    umma_commit(&bar->v_empty[s]);                    // both Q tiles have read V(i)
-                    if (i == n_tiles - 1) umma_commit(&bar->o_full);  // the output accumulators are complete
+                    umma_commit(&bar->kv_empty[s]);                   // both Q tiles have read V(i) and K(i+1)
+                    if (!more) umma_commit(&bar->o_full);             // the output accumulators are complete
                 }
             };
-            for (int t = 0; t < n_q && ok; ++t) issue_s(t, 0);
+            for (int t = 0; t < n_q && ok; ++t) issue_first(t);
             for (int i = 0; i < n_tiles && ok; ++i)
-                for (int t = 0; t < n_q && ok; ++t) {
-                    issue_o(t, i);
-                    if (i + 1 < n_tiles && ok) issue_s(t, i + 1);
-                }
+                for (int t = 0; t < n_q && ok; ++t) issue_pair(t, i);
         }
     } else {
         // ------------------------------------------------------------------ softmax and output
@@ -568,19 +591,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         const float m_new = move ? m_true : m_ref;
                         const float ref = m_new == -INFINITY ? 0.0f : m_new;
                         if (i > 0) {
-                            ok = mbar_wait(&bar->p_empty[t], (i & 1) ^ 1, abort_flag, 31);
-                            if (ok) {
-                                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                                const float corr = move ? fast_exp2(m_ref - ref) : 1.0f;
-                                l_run *= corr;
+                            // The accumulator is at rest: O_t(i-1) was issued before S_t(i), the tensor pipe runs them
+                            // in order, and s_full (waited for above) came when all of them had finished; O_t(i) waits
+                            // for this warp's p_full.
+                            const float corr = move ? fast_exp2(m_ref - ref) : 1.0f;
+                            l_run *= corr;
 #pragma unroll 1
-                                for (int c = 0; c < OC; c += 32) {
-                                    float v[32];
-                                    tmem_ld32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
+                            for (int c = 0; c < OC; c += 32) {
+                                float v[32];
+                                tmem_ld32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
 #pragma unroll
-                                    for (int e = 0; e < 32; ++e) v[e] *= corr;
-                                    tmem_st32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
-                                }
+                                for (int e = 0; e < 32; ++e) v[e] *= corr;
+                                tmem_st32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
                             }
                         } else if (move) {
                             l_run *= fast_exp2(m_ref - ref);         // first tile: nothing accumulated yet (and l_run is 0)
