@@ -51,6 +51,8 @@ def peaks():
             out["hbm_gbs"] = float(d["hbm_gbs"])
         if "bf16_tflops" in d:
             out["bf16_tflops"] = float(d["bf16_tflops"])
+        if "bf16_tflops_sustained" in d:                 # the same product looped for seconds under the power cap
+            out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
         out["source"] = "measured"
     except (OSError, ValueError):
         pass
@@ -396,6 +398,9 @@ def main() -> int:
     prefill_flops = 2 * T * L * per_layer + 2 * V * H + L * 4 * nh * hd * T * (T + 1) / 2
     prefill = {"value": round(T * 1000.0 / prefill_ms, 1), "tokens": T, "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    if "bf16_tflops_sustained" in pk:
+        prefill["frac_sustained"] = round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     value = args.batch * 1000.0 / ms
     rec = {

@@ -130,17 +130,20 @@ def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) 
         name, defines = split_key(n)
         cmd = [nvcc, *NVCC_FLAGS, *defines, *(extra_flags or []), "-I", CSRC, "-o", tmp, os.path.join(CSRC, SOURCES[name])]
         _log(f"compiling {SOURCES[name]} {' '.join(defines)} for sm_100a ...".replace("  ", " "))
-        procs[n] = (subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True), tmp)
+        log = tempfile.TemporaryFile(mode="w+")          # not a pipe: a long error listing must not block nvcc
+        procs[n] = (subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT, text=True), tmp, log)
     last = time.time()
     pending = dict(procs)
     while pending:
-        for n, (p, tmp) in list(pending.items()):
+        for n, (p, tmp, log) in list(pending.items()):
             if p.poll() is None:
                 continue
-            out = p.stdout.read() if p.stdout else ""
+            log.seek(0)
+            out = log.read()
+            log.close()
             del pending[n]
             if p.returncode != 0:
-                for _, (q, qtmp) in pending.items():
+                for _, (q, _qtmp, _qlog) in pending.items():
                     q.kill()
                 raise BuildError(f"nvcc failed on {n} (exit {p.returncode}):\n{out}")
             os.replace(tmp, paths[n])
