@@ -136,3 +136,39 @@ def test_trace_run_program(tmp_path, dtype):
             k += len(w)
         assert k == arr.shape[0]
     compare({r: torch.cat(v) for r, v in rows.items()}, ref, tol, f"trace_run/{dtype}")
+
+
+# many heads of 32 and a long prompt: a step of more than a thousand tokens takes the kernels that only large
+# steps take (QK norm + RoPE + cache write with a warp per token and run of heads; the tcgen05 product when its
+# tiles fill the GPU, which a model this small never does, so the test switches it on)
+LONG_PROMPT = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 1, "hidden_size": 64,
+    "num_attention_heads": 16, "num_key_value_heads": 8, "head_dim": 32, "intermediate_size": 96,
+    "vocab_size": 300, "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 1600, "hidden_act": "silu",
+}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("products", ["auto", "tcgen05"])
+def test_long_prompt_in_one_step_gpu(tmp_path, dtype, products):
+    d = make_model_dir(str(tmp_path / "m"), LONG_PROMPT, seed=21, dtype="bfloat16", sharpen=2.0)
+    reqs = {"long": random_ids(1500, LONG_PROMPT["vocab_size"], 7), "short": random_ids(40, LONG_PROMPT["vocab_size"], 8)}
+    plain = PlainQwen3(d)
+    ref = {r: plain.logits(ids) for r, ids in reqs.items()}
+    tol = TOL_F32
+    if dtype == "bfloat16":
+        rounded = PlainQwen3(d, round_to=torch.bfloat16)
+        ref16 = {r: rounded.logits(ids) for r, ids in reqs.items()}
+        tol, ref = bf16_tolerance(ref16, ref), ref16
+    # both requests in one step of 1,540 tokens; then the long one again in two steps (1,300 + 200)
+    both = [([(r, ids, list(range(len(ids)))) for r, ids in reqs.items()], list(reqs))]
+    ids = reqs["long"]
+    cut = [([("long", ids[:1300], list(range(1300)))], []), ([("long", ids[1300:], list(range(200)))], ["long"])]
+    for what, steps in (("one step", both), ("two steps", cut)):
+        eng = engine_for(d, dtype, max_live_tokens(steps, 64), page_size=64)
+        eng.ops.plain_gemm = products
+        got = replay(eng, steps, poison=True)
+        compare(got, {r: ref[r] for r in got}, tol, f"long prompt/{dtype}/{products}/{what}")
+        eng.check_kernels()
