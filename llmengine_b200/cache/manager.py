@@ -298,6 +298,17 @@ class CacheManager:
             g.committed -= st.committed[gi]
         self._free_slots.append(st.slot)
 
+    def forget_request(self, req: Hashable) -> None:
+        """Undo `add_request` for a request that never ran: it must hold no pages."""
+        st = self.requests.pop(req, None)
+        if st is None:
+            raise CacheError(f"request {req!r} is not live")
+        if any(p >= 0 for b in st.blocks for p in b) or any(st.committed):
+            raise CacheError(f"request {req!r} holds pages or promises: it cannot be forgotten")
+        self._free_slots.append(st.slot)
+        if st.slot in self._new_slots:
+            self._new_slots.remove(st.slot)
+
     # ------------------------------------------------------------------ admission control
     def try_commit(self, req: Hashable, total_tokens: int, max_portion: int) -> bool:
         """Promise the request the pages it will need at its peak, in every group, or promise nothing.

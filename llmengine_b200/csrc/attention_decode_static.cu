@@ -26,8 +26,9 @@ LLME_API int llme_attention_decode_static(const LlmeDecodeArgs* public_args, cud
     if (!public_args) LLME_REFUSE("attention_decode_static: null argument block");
     FastAttnArgs a = *reinterpret_cast<const FastAttnArgs*>(public_args);
     if (a.n_rows <= 0) return 0;
+    if (a.nh <= 0 || a.splits < 1) LLME_REFUSE("attention_decode_static: %d heads, %d splits: both must be positive", a.nh, a.splits);
     const long long need = llme_attention_decode_scratch_floats(a.n_rows, a.nh, a.splits);
-    if (a.n_rows < 0 || a.nh <= 0 || a.splits < 1 || need > (long long)LLME_STATIC_SCRATCH_FLOATS)
+    if (need > (long long)LLME_STATIC_SCRATCH_FLOATS)
         LLME_REFUSE("attention_decode_static: %d requests x %d heads x %d splits need %lld scratch values, "
                     "the built-in array holds %d; use fewer splits or llme_attention_decode with your own buffer",
                     a.n_rows, a.nh, a.splits, need, (int)LLME_STATIC_SCRATCH_FLOATS);

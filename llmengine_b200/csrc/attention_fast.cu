@@ -520,6 +520,10 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cl_rank));
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(cl_size));
     const bool clustered = cl_size > 1;
+    // A block may store into the first block's shared memory only once that block is known to run.  Every
+    // block of the cluster arrives here, at its very start, and waits for the others just before its first
+    // remote store; by then the key/value loop has hidden the wait.
+    if (clustered) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     const int zi = blockIdx.z;
     const int r = a.rows[zi];
@@ -680,6 +684,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
         }
     }
     __syncthreads();
+    if (clustered) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");     // all blocks of the cluster have started
     for (int row = warp; row < rows_here; row += 4) {
         float mm = -INFINITY;
 #pragma unroll
@@ -844,15 +849,6 @@ constexpr size_t PORTION_SMEM = (size_t)(BM + 2 * BN) * LDS * sizeof(bf16);
 constexpr size_t DECODE_SMEM = (size_t)(16 * LDS + 4 * DSTAGES * STAGE_ELEMS) * sizeof(bf16) + (size_t)CL_SLOTS * PART * sizeof(float);
 static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)4 * DSTAGES * STAGE_ELEMS * sizeof(bf16), "the merge buffer must fit the stage buffers");
 
-// LLME_DECODE_CLUSTER=0: the splits always merge through global memory (for comparisons)
-bool cluster_merge_disabled() {
-    static const bool off = [] {
-        const char* e = getenv("LLME_DECODE_CLUSTER");
-        return e && e[0] == '0';
-    }();
-    return off;
-}
-
 int check_common(const FastAttnArgs& a, bool fused = false) {
     if ((!a.q && !fused) || !a.cache || !a.out || !a.rows || !a.cu_q_lens || !a.ctx_lens || !a.table_rows || !a.block_tables)
         LLME_REFUSE("attention: null pointer");
@@ -906,7 +902,7 @@ static int launch_decode(const FastAttnArgs& a, const FusedQkv& f, cudaStream_t 
     dim3 grid(a.splits, a.nkv * chunks, a.n_rows);
     if ((long long)a.n_rows * a.nkv * chunks > COUNTER_WORDS) LLME_REFUSE("attention: more than %d (request, head) pairs in one split launch", COUNTER_WORDS);
     const int rows_cap = G < 16 ? G : 16;
-    if (a.splits >= 2 && a.splits <= 8 && a.splits * rows_cap <= CL_SLOTS && !cluster_merge_disabled()) {
+    if (a.splits >= 2 && a.splits <= 8 && a.splits * rows_cap <= CL_SLOTS) {
         // the splits of a (request, key/value head) as one thread-block cluster: they merge through the first
         // block's shared memory
         cudaLaunchConfig_t cfg = {};

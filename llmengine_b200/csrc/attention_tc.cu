@@ -61,10 +61,7 @@ constexpr int HALVES = HD / 64;        // 64-column (128-byte) halves of a row
 constexpr int BM = 128;                // rows per Q tile
 constexpr int QT = 2;                  // Q tiles per block: they share every key/value tile the block loads
 constexpr int BN = 128;                // keys per tile
-#ifndef LLME_TC_BOX_ROWS
-#define LLME_TC_BOX_ROWS 32
-#endif
-constexpr int BOX_ROWS = LLME_TC_BOX_ROWS;   // most keys one TMA load brings; a tile's loads are started by as many lanes
+constexpr int BOX_ROWS = 32;           // most keys one TMA load brings; a tile's loads are started by as many lanes
 constexpr int THREADS = 32 * (2 + 8 * QT);   // producer, matrix warp, eight softmax warps per Q tile
 constexpr int HALF_BYTES = 128 * 128;  // a [128 rows x 64 columns] bfloat16 tile with 128-byte rows
 constexpr int TILE_BYTES = HALVES * HALF_BYTES;
@@ -238,20 +235,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// Diagnostic build (-DLLME_TC_TRACE): the first block writes the time of its pipeline events, tile by tile.
-#ifdef LLME_TC_TRACE
-__device__ unsigned long long g_trace[16][64];
-__device__ __forceinline__ void trace(int what, int i) {
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 64) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        g_trace[what][i] = t;
-    }
-}
-#else
-__device__ __forceinline__ void trace(int, int) {}
-#endif
-
 struct Barriers {
     // kv_full / kv_empty [i % 2]: the values of key tile i together with the keys of tile i + 1, which the
     // matrix warp takes in one go; the keys of the first tile have a barrier pair of their own
@@ -367,7 +350,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (empty) ok = mbar_wait(empty, empty_parity, abort_flag, 10 + which);
             ok = ok && !*abort_flag;
             if (!ok) return;
-            if (lane == 0) trace(8 + which, i);
             // First the boxes that straddle an edge of the visible range: they are copied by hand, visible
             // rows only, the rest zeroed.  Then, after those writes are published, one lane arms the barrier
             // and the lanes start the TMA loads of the boxes that are needed whole.
@@ -394,7 +376,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (whole)
                 tma_load_2d(tile + my_half * HALF_BYTES + (my_box << box_shift) * 128, &map_kv, my_half * 64,
                             (int)(my_row + (which ? v_rows : 0)), full);
-            if (lane == 0) trace(which, i);
             __syncwarp();
         };
         // The keys run one tile ahead of the values: the matrix warp takes V(i) and K(i+1) together (O += P V(i),
@@ -454,7 +435,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (HALVES == 2) umma_qk_half<false>(d, t == 0 ? dq[0][HALVES - 1] : dq[QT - 1][HALVES - 1], dk[0][HALVES - 1], id_s);
                 if (t == n_q - 1) umma_commit(&bar->k0_empty);        // both Q tiles have read K(0)
                 umma_commit(&bar->s_full[t]);
-                trace(2 + t, 0);
             };
             // O_t(i) += P_t(i) V(i) and, straight behind it, S_t(i+1) = Q_t K(i+1)^T: every wait comes before the
             // sixteen instructions and every commit after them, so that the thread's own bookkeeping (which the
@@ -482,7 +462,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         umma_qk_half<false>(pa, t == 0 ? dq[0][HALVES - 1] : dq[QT - 1][HALVES - 1], s1 == 0 ? dk[0][HALVES - 1] : dk[1][HALVES - 1], id_s);
                     umma_commit(&bar->s_full[t]);
                 }
-                trace(12 + t, i);
                 if (t == n_q - 1) {
                     umma_commit(&bar->kv_empty[s]);                   // both Q tiles have read V(i) and K(i+1)
                     if (!more) umma_commit(&bar->o_full);             // the output accumulators are complete
@@ -572,7 +551,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     if (with_max) own_max = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
                 };
                 if (ok) {
-                    if (warp == 2 && lane == 0) trace(4, i);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     unmasked = warp_full && j0 + BN - 1 <= warp_p_lo && j0 >= warp_lo_last;
                     half_pass(ref_old, true);
@@ -620,7 +598,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bar->p_full[t]);
-                    if (warp == 2 && lane == 0) trace(7, i);
                 }
             }
             if (ok) ok = mbar_wait(&bar->o_full, 0, abort_flag, 33);
@@ -680,12 +657,6 @@ static_assert(SMEM_BYTES <= 232448, "the block's shared memory must fit an SM");
 }  // namespace
 
 LLME_API int llme_attention_tc_head_dim() { return HD; }
-
-#ifdef LLME_TC_TRACE
-LLME_API int llme_attention_tc_trace(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 16 * 64);
-}
-#endif
 
 // Whether this kernel takes the problem: a page size that divides 128 and is at least 8 (a TMA box of whole
 // pages with whole swizzle groups), and a group size (query heads per key/value head) that divides 128.

@@ -48,8 +48,8 @@ inline char* llme_error_buffer() {
 // environment: measured inside CUDA graphs on B200 (Qwen3-8B shape, batch 8) the decode step took 5.1 ms
 // with it (6.7 ms when every kernel let its successor in at its very start) and 3.85 ms without: the
 // early-resident successors take issue slots and bandwidth from the kernel on the critical path.  Switched
-// on for single source files (LLME_PDL=gemm_skinny.cu,...) or single products it stayed within the noise of
-// the step time (+-0.7%), except for the output product after the decode attention, which lost 7 us.
+// on for the kernels of single source files or single products it stayed within the noise of the step time
+// (+-0.7%), except for the output product after the decode attention, which lost 7 us.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -58,13 +58,8 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 #include <utility>
 inline bool llme_pdl_enabled() {
     static const bool on = [] {
-        const char* e = getenv("LLME_PDL");   // "1": every kernel; else a list of source files, e.g. "gemm_skinny.cu,elementwise.cu"
-        if (!e) return false;
-        if (e[0] == '1') return true;
-        const char* base = __BASE_FILE__;
-        for (const char* p = base; *p; ++p)
-            if (*p == '/') base = p + 1;
-        return strstr(e, base) != nullptr;
+        const char* e = getenv("LLME_PDL");
+        return e && e[0] == '1';
     }();
     return on;
 }

@@ -229,6 +229,9 @@ class Engine:
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
+            if len(set(int(w) for w in e.want)) != len(e.want):
+                # the final norm adds the pending contribution into each wanted row once per mention
+                raise StepError(f"request {e.request!r}: a place is wanted twice")
         for r in end:
             if r not in seen and not self.cache.has(r):
                 raise StepError(f"request {r!r} is ended but is not live")
@@ -253,8 +256,8 @@ class Engine:
                     self.cache.add_request(e.request)
                     created.append(e.request)
                 before = [len(b) for b in self.cache.requests[e.request].blocks]
-                self.cache.reserve(e.request, s + len(e.tokens))
                 grown.append((e.request, before))
+                self.cache.reserve(e.request, s + len(e.tokens))
         except (OutOfPages, CacheError) as err:
             self._undo(created, grown)
             raise StepError(f"the step does not fit the cache: {err}") from None
@@ -395,19 +398,21 @@ class Engine:
         return logits
 
     def _undo(self, created, grown) -> None:
-        for req, before in grown:
-            if req in created:
-                continue
+        """Take back what a refused batch had reserved, last first, so that the free lists (last in, first
+        out) and the free slots stand exactly as before: the pages a later request gets do not depend on
+        whether a batch was refused in between."""
+        for req, before in reversed(grown):
             st = self.cache.requests[req]
-            for gi, n in enumerate(before):
+            for gi in reversed(range(len(before))):
+                n = before[gi]
                 extra = st.blocks[gi][n:]
                 if extra:
-                    self.cache.groups[gi].pool.free([p for p in extra if p >= 0])
+                    self.cache.groups[gi].pool.free([p for p in reversed(extra) if p >= 0])
                     del st.blocks[gi][n:]
                     self.cache.tables[gi][st.slot, n:n + len(extra)] = -1
                     self.cache._mark(gi, st.slot, n, n + len(extra))
-        for req in created:
-            self.cache.free_request(req)
+        for req in reversed(created):
+            self.cache.forget_request(req)
 
     def free(self, request: Hashable) -> None:
         self.cache.free_request(request)

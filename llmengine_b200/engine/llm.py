@@ -163,4 +163,6 @@ class LLM:
                 for out in self.scheduler.collect_finished():
                     done[out.sequence_id] = out
                 break
+        # a kernel whose bounded wait gave up has produced invalid results: never hand those out silently
+        self.engine.check_kernels()
         return [GenerationOutput(i, done[i].prompt_tokens, done[i].generated_tokens, done[i].finish_reason) for i in ids]

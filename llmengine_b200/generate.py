@@ -3,10 +3,16 @@
 max_tokens 64, greedy, progress on stderr, result on stdout, `[Generated N tokens total]`).
 
     python -m llmengine_b200.generate <model_dir> [prompt] [max_tokens] [options]
+    python -m llmengine_b200.generate --random-config config.json --seed 7 [prompt] [max_tokens] [options]
 
 This engine works on token ids (it has no tokenizer), so `prompt` is a list of ids separated by
-commas or spaces, default "1".  Several prompts may be given separated by ';'.  The sampling
-options carry the names of the reference's SamplingConfig fields.
+commas or spaces, default "1".  Several prompts may be given separated by ';', or one a line in
+a file (`--prompt-ids-file`).  The sampling options carry the names of the reference's
+SamplingConfig fields.  With `--random-config` the model is a config.json alone: its weights are
+drawn from `--seed` (the folder that `python -m llmengine_b200.make_random_model` would write,
+made in a temporary place).  `--print-logits N` also prints, for each prompt, the N largest
+logits at its last prompt token (token:value pairs), which the reference's Sampler::get_top_tokens
+gives (src/runtime/sampler.cpp:143-197).
 """
 from __future__ import annotations
 
@@ -31,9 +37,14 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .config import EngineConfig
 
     ap = argparse.ArgumentParser(prog="generate", description=__doc__.split("\n\n")[0])
-    ap.add_argument("model", help="folder with config.json and model.safetensors")
+    ap.add_argument("model", nargs="?", default=None, help="folder with config.json and model.safetensors")
     ap.add_argument("prompt", nargs="?", default="1", help="token ids, e.g. \"5,17,3\"; ';' separates prompts")
     ap.add_argument("max_tokens", nargs="?", type=int, default=64)
+    ap.add_argument("--random-config", default=None, metavar="CONFIG.json",
+                    help="instead of a model folder: a config.json whose weights are drawn from --seed")
+    ap.add_argument("--prompt-ids-file", default=None, help="file with one prompt (token ids) a line")
+    ap.add_argument("--print-logits", type=int, default=0, metavar="N",
+                    help="print the N largest logits at each prompt's last token")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--greedy", dest="greedy", action="store_true", default=True)
     ap.add_argument("--no-greedy", dest="greedy", action="store_false", help="draw from the distribution")
@@ -57,7 +68,26 @@ def main(argv: Optional[List[str]] = None) -> int:
     def log(msg: str) -> None:
         print(msg, file=sys.stderr, flush=True)
 
-    prompts = parse_prompts(args.prompt)
+    if args.random_config is not None:
+        # with --random-config the first two positionals are the prompt and max_tokens
+        if args.model is not None:
+            args.prompt, args.max_tokens = args.model, (int(args.prompt) if args.prompt != "1" else args.max_tokens)
+        import json
+        import tempfile
+
+        from .config import config_from_dict
+        from .weights import write_random_model
+        with open(args.random_config, "r", encoding="utf-8") as f:
+            config = config_from_dict(json.load(f))
+        holder = tempfile.TemporaryDirectory(prefix="llmengine_b200_random_")
+        args.model = write_random_model(config, args.seed, holder.name)
+    elif args.model is None:
+        ap.error("a model folder (or --random-config) is needed")
+    if args.prompt_ids_file is not None:
+        with open(args.prompt_ids_file, "r", encoding="utf-8") as f:
+            prompts = parse_prompts(";".join(line.strip() for line in f if line.strip()))
+    else:
+        prompts = parse_prompts(args.prompt)
     log("[1/3] Loading model...")
     t0 = time.time()
     llm = LLM(args.model, dtype=args.dtype, page_size=args.page_size, max_cached_tokens=args.max_cached_tokens,
@@ -66,6 +96,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     log(f"      {time.time() - t0:.1f} s")
     sp = SamplingParams(greedy=args.greedy, top_k=args.top_k, top_p=args.top_p, temperature=args.temperature,
                         repetition_penalty=args.repetition_penalty, seed=args.seed)
+    if args.print_logits > 0:
+        from .engine.engine import StepEntry
+        for i, p in enumerate(prompts):
+            row = llm.engine.step([StepEntry(("logits", i), p, [len(p) - 1])], end=[("logits", i)])[0]
+            top = row.topk(min(args.print_logits, row.numel()))
+            print("logits " + " ".join(f"{int(t)}:{float(v):.6f}" for v, t in zip(top.values.tolist(), top.indices.tolist())))
     log(f"[2/3] Generating ({len(prompts)} prompt(s), up to {args.max_tokens} tokens each)...")
     t0 = time.time()
     outs = llm.generate(prompts, sp, args.max_tokens, eos_token_id=None if args.ignore_eos else "model")

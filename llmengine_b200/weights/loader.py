@@ -89,24 +89,62 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little") & (2**63 - 1)
 
 
+def _signed(c: int) -> int:
+    return c - (1 << 64) if c >= (1 << 63) else c
+
+
+_GAMMA, _M1, _M2 = _signed(0x9E3779B97F4A7C15), _signed(0xBF58476D1CE4E5B9), _signed(0x94D049BB133111EB)
+
+
+def _mix64(z: torch.Tensor) -> torch.Tensor:
+    """The splitmix64 finaliser on int64 tensors (products wrap modulo 2^64; shifts are made logical by masking)."""
+    z = (z ^ ((z >> 30) & ((1 << 34) - 1))) * _M1
+    z = (z ^ ((z >> 27) & ((1 << 37) - 1))) * _M2
+    return z ^ ((z >> 31) & ((1 << 33) - 1))
+
+
+def counter_normal(key: int, start: int, count: int, device: torch.device) -> torch.Tensor:
+    """Elements start..start+count-1 of the stream of `key`: 32-bit variates with mean 0 and variance 1, each
+    a function of (key, element index) alone.  An element is the sum of twelve 16-bit uniform integers cut from
+    three hashes of its counter, centred: integer arithmetic until the last step, so every device, library
+    version and chunking gives the same bits.  (The sum of twelve uniforms is the classic stand-in for a normal
+    variate: right mean, variance and symmetry, tails that end at six standard deviations.)"""
+    idx = torch.arange(start, start + count, dtype=torch.int64, device=device)
+    base = idx * _GAMMA + _signed(key & ((1 << 64) - 1))
+    total = torch.zeros(count, dtype=torch.int64, device=device)
+    for j in range(3):
+        h = _mix64(base + _signed((0xD1B54A32D192ED03 * (j + 1)) & ((1 << 64) - 1)))
+        for k in range(4):
+            total += (h >> (16 * k)) & 0xFFFF
+    # 12 uniforms on {0..65535}: mean 12 * 32767.5 = 393210, variance 12 * (65536^2 - 1) / 12 ~ 65536^2
+    return (total - 393210).to(torch.float32) * (1.0 / 65536.0)
+
+
 def random_tensor(name: str, spec: WeightSpec, seed: int, device: torch.device = torch.device("cpu")) -> torch.Tensor:
-    """A tensor drawn from (seed, name) alone, so values do not depend on the order of generation:
-    "normal" ~ N(0, 0.02), "gain" ~ 1 + N(0, 0.1), 32-bit.  (CPU and CUDA generators give
-    different streams; a model folder is always written from the CPU stream.)"""
-    g = torch.Generator(device=device)
-    g.manual_seed(_tensor_seed(seed, name))
-    z = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
+    """A 32-bit tensor drawn from (seed, name, element index) alone, so that its values depend neither on the
+    order of generation nor on the device that makes them: "normal" ~ N(0, 0.02), "gain" ~ 1 + N(0, 0.1)."""
+    numel = 1
+    for d in spec.shape:
+        numel *= int(d)
+    key = _tensor_seed(seed, name)
+    out = torch.empty(numel, dtype=torch.float32, device=device)
+    step = 1 << 24                                         # bounded temporaries for the large tables
+    for a in range(0, numel, step):
+        n = min(step, numel - a)
+        out[a:a + n] = counter_normal(key, a, n, device)
+    out = out.view(tuple(spec.shape))
     if spec.init == "gain":
-        return 1.0 + 0.1 * z
+        return 1.0 + 0.1 * out
     if spec.init == "normal":
-        return 0.02 * z
+        return 0.02 * out
     raise ValueError(f"tensor {name!r}: unknown init {spec.init!r}")
 
 
 def random_model_weights(model, seed: int, compute: torch.dtype, device: torch.device,
                          file_dtype: torch.dtype = torch.bfloat16) -> None:
-    """Fill a model with random weights directly on the device (no folder is written).
-    Values pass through `file_dtype` as they would through a file."""
+    """Fill a model with random weights directly on the device (no folder is written): the tensors that
+    `write_random_model` would store for the same seed, bit for bit.  Values pass through `file_dtype` as
+    they would through a file."""
     tensors = {}
     for name, spec in model.weight_specs().items():
         t = random_tensor(name, spec, seed, device).to(file_dtype)
@@ -114,19 +152,43 @@ def random_model_weights(model, seed: int, compute: torch.dtype, device: torch.d
     model.load_weights(tensors)
 
 
-def write_random_model(config, seed: int, out_dir: str, dtype: str = "bfloat16") -> str:
-    """Random-weights mode: write `config.json` and `model.safetensors` for a configuration and a seed."""
+def write_random_model(config, seed: int, out_dir: str, dtype: str = "bfloat16", shard_bytes: int = 0,
+                       device: str = "cpu") -> str:
+    """Random-weights mode: write `config.json` and `model.safetensors` for a configuration and a seed.
+    `shard_bytes` > 0 writes `model-0000i-of-0000n.safetensors` files of about that size with a
+    `model.safetensors.index.json` instead, as large checkpoints are laid out.  `device`: where the values
+    are computed (they are the same everywhere; a GPU is only faster for large tables)."""
     from ..engine.model import Model
     from ..parts.base import Runtime
 
     file_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
     os.makedirs(out_dir, exist_ok=True)
     model = Model(config.model_spec(), Runtime(None, torch.device("cpu"), torch.float32, 1))
-    tensors = {n: random_tensor(n, s, seed).to(file_dtype) for n, s in model.weight_specs().items()}
+    dev = torch.device(device)
+    tensors = {n: random_tensor(n, s, seed, dev).to(file_dtype).cpu() for n, s in model.weight_specs().items()}
     d = config.to_dict()
     d["torch_dtype"] = dtype
     with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(d, f, indent=2)
-    write_safetensors(os.path.join(out_dir, "model.safetensors"), tensors,
-                      {"format": "pt", "seed": str(seed)})
+    meta = {"format": "pt", "seed": str(seed)}
+    if shard_bytes <= 0:
+        write_safetensors(os.path.join(out_dir, "model.safetensors"), tensors, meta)
+        return out_dir
+    shards, size = [[]], 0
+    for n in sorted(tensors):
+        b = tensors[n].numel() * tensors[n].element_size()
+        if shards[-1] and size + b > shard_bytes:
+            shards.append([])
+            size = 0
+        shards[-1].append(n)
+        size += b
+    weight_map, total = {}, 0
+    for i, names in enumerate(shards):
+        fn = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        write_safetensors(os.path.join(out_dir, fn), {n: tensors[n] for n in names}, meta)
+        for n in names:
+            weight_map[n] = fn
+            total += tensors[n].numel() * tensors[n].element_size()
+    with open(os.path.join(out_dir, "model.safetensors.index.json"), "w", encoding="utf-8") as f:
+        json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=2)
     return out_dir

@@ -110,15 +110,29 @@ def poison_free_pages(engine) -> None:
                 engine.cache.kv[run][free] = float("nan")
 
 
-def replay(engine, steps: List[Step], poison: bool = False) -> Dict[str, torch.Tensor]:
-    """Run a trace through `engine.step`; returns request -> [positions, vocab] logits in position order."""
+def replay(engine, steps: List[Step], poison: bool = False, page_log: Optional[Dict[str, set]] = None,
+           tamper=None) -> Dict[str, torch.Tensor]:
+    """Run a trace through `engine.step`; returns request -> [positions, vocab] logits in position order.
+    `page_log` collects, per request, every page of cache group 0 it ever held.  `tamper(engine, i)` is
+    called before step i (the negative controls damage the cache there)."""
     from llmengine_b200.engine.engine import StepEntry
 
     rows: Dict[str, List[torch.Tensor]] = {}
-    for entries, end in steps:
+    for i, (entries, end) in enumerate(steps):
+        if tamper is not None:
+            tamper(engine, i)
         if poison:
             poison_free_pages(engine)
-        out = engine.step([StepEntry(r, t, w) for r, t, w in entries], end)
+        if page_log is not None:
+            # what the step will hold: reserve as the step does, by looking after it (ended requests are gone
+            # by then, so look at the tables before they are freed: run the step without `end`, then end them)
+            out = engine.step([StepEntry(r, t, w) for r, t, w in entries], [])
+            for r, _, _ in entries:
+                page_log.setdefault(r, set()).update(p for p in engine.cache.requests[r].blocks[0] if p >= 0)
+            for r in end:
+                engine.free(r)
+        else:
+            out = engine.step([StepEntry(r, t, w) for r, t, w in entries], end)
         k = 0
         for r, t, w in entries:
             if w:
@@ -163,11 +177,50 @@ def compare(got: Dict[str, torch.Tensor], ref: Dict[str, torch.Tensor], tol: flo
 
 
 def engine_for(model_dir: str, dtype: str, pool_tokens: int, page_size: int = 16, ops=None, device: str = "cuda:0",
-               kernels: str = "fast", max_requests: int = 8, **more) -> "Engine":
+               kernels: str = "fast", max_requests: int = 8, use_cuda_graphs: bool = False, **more) -> "Engine":
     from llmengine_b200.engine.engine import Engine
 
     pool = -(-pool_tokens // page_size) * page_size
     ec = EngineConfig(dtype=dtype, page_size=page_size, max_cached_tokens=pool, max_num_seqs=max_requests,
                       max_num_batched_tokens=pool, prefill_chunk=pool, device=device, kernels=kernels,
-                      use_cuda_graphs=False, **more)
+                      use_cuda_graphs=use_cuda_graphs, **more)
     return Engine(model_dir, engine_config=ec, ops=ops)
+
+
+def eos_scenario(make_llm, prompts: List[List[int]], max_tokens: int = 12):
+    """Requests that end on an end-of-sequence token at different steps while others go on and some wait for
+    admission.  A first greedy run without any end token gives each request's tokens; request i then gets as its
+    end token the one it generated at place `cut[i]` (place 0: it ends before it has generated anything; None: it
+    runs to max_tokens), so the expected output is its tokens up to the first occurrence of that token.  Returns
+    (expected, with pipelined decoding, without) as lists of (tokens, finish_reason), and the last engine used."""
+    free_run = make_llm(True)
+    base = [o.token_ids for o in free_run.generate(prompts, None, max_tokens=max_tokens, eos_token_id=None)]
+    cuts = [2, 5, 0, 9, None, 3, 7, 1]
+    expected, eos = [], []
+    for i, toks in enumerate(base):
+        cut = cuts[i % len(cuts)]
+        if cut is None:
+            eos.append(None)
+            expected.append((toks, "length"))
+        else:
+            e = toks[cut]
+            eos.append(e)
+            expected.append((toks[:toks.index(e)], "eos"))
+    runs = []
+    for pipelined in (True, False):
+        llm = make_llm(pipelined)
+        ids = [llm.add_request(p, None, max_tokens=max_tokens, eos_token_id=e) for p, e in zip(prompts, eos)]
+        done = {}
+        for _ in range(10000):
+            for out in llm.step():
+                done[out.sequence_id] = out
+            if len(done) == len(ids) and llm._inflight is None:
+                break
+        assert len(done) == len(ids), "some request never finished"
+        llm.step()                                            # nothing left: must be harmless
+        runs.append([(done[i].generated_tokens, done[i].finish_reason) for i in ids])
+        llm.engine.cache.check_invariants()
+        assert not llm.engine.cache.requests and llm.scheduler.all_done()
+        assert all(g.pool.free_count == g.pool.num_pages and g.committed == 0 for g in llm.engine.cache.groups)
+        assert llm.engine.cache.free_slots == llm.engine.cache.max_requests
+    return expected, runs[0], runs[1], base

@@ -59,8 +59,9 @@ def test_eos_and_bad_ids(tmp_path):
     llm = LLM(d, dtype="float32", max_cached_tokens=256, max_num_seqs=2, max_num_batched_tokens=64, device="cpu",
               ops=HostOps(), use_cuda_graphs=False)
     first = llm.generate([3, 4, 5], max_tokens=4, eos_token_id=None)[0].token_ids
-    out = llm.generate([3, 4, 5], max_tokens=4, eos_token_id=first[1])[0]
-    assert out.token_ids == first[:1] and out.finish_reason == "eos"
+    eos = first[1]
+    out = llm.generate([3, 4, 5], max_tokens=4, eos_token_id=eos)[0]
+    assert out.token_ids == first[:first.index(eos)] and out.finish_reason == "eos"
     with pytest.raises(ValueError, match="vocabulary"):
         llm.generate([3, 512], max_tokens=2)
 
@@ -70,3 +71,21 @@ def test_prompt_parsing():
     assert parse_prompts("1 2 3; 4,5") == [[1, 2, 3], [4, 5]]
     with pytest.raises(ValueError):
         parse_prompts(" ; ")
+
+
+def test_requests_that_end_on_eos_at_different_steps_with_pipelined_decoding(tmp_path):
+    """4 live requests and 2 waiting; end tokens picked so that requests end at different steps, one of them
+    before its first token.  Pipelined decoding learns of an end one step late: the wasted token must be
+    dropped, the pages freed, the waiting requests admitted, and the tokens equal to the unpipelined run's."""
+    from helpers import eos_scenario
+    d = make_model_dir(str(tmp_path / "m"), TINY_B, 15, dtype="float32", sharpen=2.0)
+    mk = lambda pipelined: LLM(d, dtype="float32", page_size=8, max_cached_tokens=512, max_num_seqs=4,
+                               max_num_batched_tokens=64, prefill_chunk=48, device="cpu", ops=HostOps(),
+                               use_cuda_graphs=False, pipeline_decode=pipelined)
+    prompts = [random_ids(n, 1000, 40 + i) for i, n in enumerate([9, 70, 3, 25, 1, 50])]
+    expected, piped, plain_run, base = eos_scenario(mk, prompts)
+    assert piped == expected and plain_run == expected
+    assert len({len(t) for t, _ in expected}) >= 4, "the requests should end at different steps"
+    plain = PlainQwen3(d)
+    for p, toks in zip(prompts, base):
+        assert toks == plain_generate(plain, p, len(toks))

@@ -139,3 +139,22 @@ def test_command_line(tmp_path):
     plain = PlainQwen3(d)
     for prompt, line in zip(([5, 17, 3], [9, 8, 7, 6]), lines):
         _check_greedy(plain, prompt, [int(x) for x in line.split()], 1e-4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_requests_that_end_on_eos_at_different_steps_with_pipelined_decoding(tmp_path, dtype, graphs):
+    """4 live requests and 2 waiting, end tokens picked so that the requests end at different steps (one before its
+    first token): pipelined decoding, which learns of an end one step late, gives the tokens of the unpipelined run,
+    frees every page and admits the waiting requests."""
+    from helpers import eos_scenario
+    d = make_model_dir(str(tmp_path / "m"), TINY_B, 15, dtype="bfloat16", sharpen=1.5)
+    mk = lambda pipelined: LLM(d, dtype=dtype, page_size=8, max_cached_tokens=512, max_num_seqs=4, max_num_batched_tokens=64,
+                               prefill_chunk=48, use_cuda_graphs=graphs, pipeline_decode=pipelined)
+    prompts = [random_ids(n, 1000, 40 + i) for i, n in enumerate([9, 70, 3, 25, 1, 50])]
+    expected, piped, unpiped, base = eos_scenario(mk, prompts)
+    assert piped == expected and unpiped == expected
+    assert len({len(t) for t, _ in expected}) >= 4
+    plain = PlainQwen3(d)
+    for p, toks in zip(prompts, base):
+        _check_greedy(plain, p, toks, 1e-4 if dtype == "float32" else 3e-2)

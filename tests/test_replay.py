@@ -78,11 +78,18 @@ def _run_all(tmp_path, name, dtype, sharpen, ops, device, page_size=None):
     for what, steps in _traces(reqs).items():
         pool = max_live_tokens(steps, 64)
         eng = engine_for(d, dtype, pool, page_size=page, ops=ops, device=device)
-        got = replay(eng, steps, poison=True)
-        worst[what] = compare(got, ref, tol, f"{name}/{dtype}/{what}")
+        pages = {} if what == "mixed" else None
+        got = replay(eng, steps, poison=True, page_log=pages)
+        worst[what] = compare(got, ref, tol, f"{name}/{dtype}/{what}") / tol
         eng.cache.check_invariants()
         assert not eng.cache.requests, "every request was ended, nothing may be held"
         assert all(g.pool.free_count == g.pool.num_pages for g in eng.cache.groups)
+        if pages is not None:
+            owners = {}
+            for r, held in pages.items():
+                for p in held:
+                    owners.setdefault(p, set()).add(r)
+            assert any(len(o) > 1 for o in owners.values()), "no page was handed to a second request: the pool is too large"
     return worst
 
 
@@ -99,7 +106,8 @@ def test_replay_gpu(tmp_path, name, dtype, sharpen):
     """`sharpen` scales the QK-norm gains: attention becomes peaked, so that a key that is skipped,
     read from a wrong page or seen through a wrong mask moves the logits by far more than the tolerance."""
     worst = _run_all(tmp_path, name, dtype, sharpen, None, "cuda:0")
-    print(f"replay {name} {dtype} sharpen={sharpen}: " + ", ".join(f"{k} {v:.2e}" for k, v in worst.items()))
+    print(f"replay {name} {dtype} sharpen={sharpen}: distance as a share of the tolerance: "
+          + ", ".join(f"{k} {v:.2f}" for k, v in worst.items()))
 
 
 @pytest.mark.gpu
@@ -172,3 +180,113 @@ def test_long_prompt_in_one_step_gpu(tmp_path, dtype, products):
         got = replay(eng, steps, poison=True)
         compare(got, {r: ref[r] for r in got}, tol, f"long prompt/{dtype}/{products}/{what}")
         eng.check_kernels()
+
+
+# ----------------------------------------------------------------------------- negative controls
+def _tamper_plan(steps, page):
+    """A step of the mixed trace before which two live requests each hold at least one full page and both go on
+    afterwards: (step index, request 1, request 2)."""
+    held = {}
+    future = [set() for _ in steps]
+    seen = set()
+    for i in range(len(steps) - 1, -1, -1):
+        future[i] = set(seen)
+        seen |= {r for r, _, _ in steps[i][0]}
+    for i, (entries, end) in enumerate(steps):
+        ready = [r for r, n in held.items() if n >= page and r in future[i] | {e[0] for e in entries}]
+        ready = [r for r in ready if any(r == e[0] for j in range(i, len(steps)) for e in steps[j][0])]
+        if len(ready) >= 2:
+            return i, ready[0], ready[1]
+        for r, t, _ in entries:
+            held[r] = held.get(r, 0) + len(t)
+        for r in end:
+            held.pop(r, None)
+    raise AssertionError("the trace never has two live requests with a full page each")
+
+
+def _swap_page_contents(run):
+    """Exchange what the first pages of two live requests hold, in one layer's cache tensor."""
+    def tamper(eng, i, plan={}):
+        if i != tamper.at:
+            return
+        a = eng.cache.requests[tamper.r1].blocks[0][0]
+        b = eng.cache.requests[tamper.r2].blocks[0][0]
+        kv = eng.cache.kv[eng.cache.groups[0].runs[run]]
+        keep = kv[a].clone()
+        kv[a] = kv[b]
+        kv[b] = keep
+    return tamper
+
+
+def _swap_table_entries():
+    """Exchange the first block-table entries of two live requests (host and device tables alike): from then on
+    each reads, and owns, the other's first page in every layer of the group."""
+    def tamper(eng, i):
+        if i != tamper.at:
+            return
+        c = eng.cache
+        s1, s2 = c.requests[tamper.r1], c.requests[tamper.r2]
+        s1.blocks[0][0], s2.blocks[0][0] = s2.blocks[0][0], s1.blocks[0][0]
+        c.tables[0][s1.slot, 0], c.tables[0][s2.slot, 0] = s1.blocks[0][0], s2.blocks[0][0]
+        c._mark(0, s1.slot, 0, 1)
+        c._mark(0, s2.slot, 0, 1)
+    return tamper
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("damage", ["page_contents", "table_entries"])
+@pytest.mark.parametrize("dtype,sharpen", [("float32", 3.0), ("bfloat16", 2.0)])
+@pytest.mark.parametrize("page_size", [None, 64])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+def test_a_wrong_page_is_seen_at_the_tolerance_of_the_replay_tests(tmp_path, name, dtype, sharpen, page_size, damage):
+    """The negative control of the tests above: the same mixed trace, the same tolerance, but before one step a
+    page of one request is exchanged with a page of another (its contents in one layer, or the two block-table
+    entries).  Nothing faults (all memory is valid and held); the comparison must fail."""
+    d, page, reqs, ref, tol = _setup(tmp_path, name, dtype, sharpen)
+    page = page_size or page
+    steps = _traces(reqs)["mixed"]
+    try:
+        at, r1, r2 = _tamper_plan(steps, page)
+    except AssertionError:
+        pytest.skip("with pages this large no two requests of the trace hold a full page at the same time")
+    tamper = _swap_page_contents(0) if damage == "page_contents" else _swap_table_entries()
+    tamper.at, tamper.r1, tamper.r2 = at, r1, r2
+    eng = engine_for(d, dtype, max_live_tokens(steps, 64) + 2 * page, page_size=page)
+    got = replay(eng, steps, tamper=tamper)
+    worst = max(float((got[r] - ref[r]).abs().max()) for r in ref)
+    print(f"negative control {name} {dtype} page {page} {damage}: distance {worst / tol:.1f} x the tolerance")
+    with pytest.raises(AssertionError, match="max .diff."):
+        compare(got, ref, tol, "damaged")
+
+
+# ----------------------------------------------------------------------------- captured decode steps
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("short_context", [8192, 48])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_logits_of_captured_decode_steps(tmp_path, monkeypatch, name, dtype, short_context):
+    """Decode steps replayed from CUDA graphs give the plain implementation's logits: most of each request in one
+    step and its last 32 tokens one by one, and a long run of single-token steps of two requests side by side.  With
+    the small limit the requests grow past it while they decode, so both kinds of capture (launch shapes for short
+    contexts, and for any context) are made and replayed."""
+    from llmengine_b200.engine.engine import Engine
+    monkeypatch.setattr(Engine, "SHORT_CONTEXT", short_context)
+    d, page, reqs, ref, tol = _setup(tmp_path, name, dtype, 2.0)
+    steps = trace_bulk_then_single(reqs, 32)
+    eng = engine_for(d, dtype, max_live_tokens(steps, 64), page_size=page, use_cuda_graphs=True, max_model_len=256)
+    got = replay(eng, steps, poison=True)
+    compare(got, ref, tol, f"graphs/{name}/{dtype}/bulk_then_single")
+    assert eng._graphs, "no decode step was captured"
+    assert {k[1] for k in eng._graphs} == ({True, False} if short_context == 48 else {False})
+    # two requests side by side, one token a step from the first token on
+    ids = {r: reqs[r] for r in list(reqs)[:2]}
+    n = max(len(v) for v in ids.values())
+    side = []
+    for i in range(n):
+        entries = [(r, v[i:i + 1], [0]) for r, v in ids.items() if i < len(v)]
+        side.append((entries, [r for r, v in ids.items() if i == len(v) - 1]))
+    got = replay(eng, side, poison=True)
+    compare(got, {r: ref[r] for r in ids}, tol, f"graphs/{name}/{dtype}/side by side")
+    assert any(k[0] == 2 for k in eng._graphs)
+    eng.cache.check_invariants()
+    eng.check_kernels()

@@ -143,3 +143,90 @@ def test_random_weights_mode(tmp_path):
     f32 = SafetensorsFile(os.path.join(write_random_model(c, 9, str(tmp_path / "d"), dtype="float32"), "model.safetensors"))
     assert f32.dtype("lm_head.weight") == torch.float32
     assert torch.equal(f32.tensor("lm_head.weight").to(torch.bfloat16), fa.tensor("lm_head.weight"))
+
+
+def test_random_values_depend_on_seed_name_and_element_only():
+    """Counter-based: any slice of a tensor's stream can be made alone, the engine's on-device weights are the
+    file's tensors bit for bit, and nothing depends on the order in which tensors are made."""
+    from llmengine_b200.parts import WeightSpec
+    from llmengine_b200.weights.loader import _tensor_seed, counter_normal, random_tensor
+    whole = random_tensor("x.weight", WeightSpec((37, 11)), 5).reshape(-1)
+    piece = 0.02 * counter_normal(_tensor_seed(5, "x.weight"), 100, 60, torch.device("cpu"))
+    assert torch.equal(whole[100:160], piece)
+    assert not torch.equal(random_tensor("y.weight", WeightSpec((37, 11)), 5).reshape(-1), whole)
+    z = counter_normal(1, 0, 1 << 16, torch.device("cpu"))
+    assert abs(z.mean().item()) < 0.02 and abs(z.std().item() - 1.0) < 0.02 and z.abs().max().item() <= 6.0
+
+
+def test_engine_random_weights_equal_the_written_folder(tmp_path):
+    d = make_model_dir(str(tmp_path / "m"), TINY_B, 12)
+    from_file = _engine(d, "bfloat16")
+    ec = EngineConfig(dtype="bfloat16", max_cached_tokens=64, max_num_seqs=2, max_num_batched_tokens=64, device="cpu")
+    from_seed = Engine(config=TINY_B, random_seed=12, engine_config=ec, ops=HostOps())
+    for a, b in zip(from_file.model.blocks, from_seed.model.blocks):
+        assert torch.equal(a.mixer.w_qkv, b.mixer.w_qkv) and torch.equal(a.ffn.w_down, b.ffn.w_down)
+        assert torch.equal(a.mixer_norm.gain, b.mixer_norm.gain)
+    assert torch.equal(from_file.model.head.weight, from_seed.model.head.weight)
+
+
+def test_a_sharded_folder_loads_like_a_single_file(tmp_path):
+    """Large checkpoints come as model-0000i-of-0000n.safetensors with an index; the shards are found through it."""
+    c = config_from_dict(TINY_B)
+    one = write_random_model(c, 9, str(tmp_path / "one"))
+    many = write_random_model(c, 9, str(tmp_path / "many"), shard_bytes=60_000)
+    files = sorted(os.listdir(many))
+    shards = [f for f in files if f.endswith(".safetensors")]
+    assert "model.safetensors" not in files and "model.safetensors.index.json" in files and len(shards) >= 3
+    index = json.load(open(os.path.join(many, "model.safetensors.index.json")))
+    assert set(index["weight_map"].values()) == set(shards)
+    a, b = _engine(one), _engine(many)
+    for x, y in zip(a.model.blocks, b.model.blocks):
+        assert torch.equal(x.mixer.w_qkv, y.mixer.w_qkv) and torch.equal(x.ffn.w_gate_up, y.ffn.w_gate_up)
+    assert torch.equal(a.model.head.weight, b.model.head.weight)
+    # a tensor that a shard lacks is reported like any missing tensor
+    victim = index["weight_map"]["model.layers.1.mlp.down_proj.weight"]
+    path = os.path.join(many, victim)
+    f = SafetensorsFile(path)
+    kept = {n: f.tensor(n).clone() for n in f.names() if n != "model.layers.1.mlp.down_proj.weight"}
+    del f
+    write_safetensors(path, kept)
+    with pytest.raises(WeightError, match="model.layers.1.mlp.down_proj.weight"):
+        _engine(many)
+    # the same tensor in two shards is refused
+    other = next(s for s in shards if s != victim)
+    f = SafetensorsFile(os.path.join(many, other))
+    t = {n: f.tensor(n).clone() for n in f.names()}
+    del f
+    dup = next(iter(kept))
+    t[dup] = kept[dup]
+    write_safetensors(os.path.join(many, other), t)
+    with pytest.raises(WeightError, match="twice"):
+        _engine(many)
+
+
+def test_a_float16_file_loads(tmp_path):
+    d = make_model_dir(str(tmp_path / "m"), TINY_A, 3, dtype="float32")
+    want = _engine(d, "float32")
+    _rewrite(d, lambda t: [t.__setitem__(n, v.to(torch.float16)) for n, v in list(t.items())])
+    assert SafetensorsFile(os.path.join(d, "model.safetensors")).dtype("model.norm.weight") == torch.float16
+    e32, e16 = _engine(d, "float32"), _engine(d, "bfloat16")
+    w = want.model.blocks[0].ffn.w_down
+    assert e32.model.blocks[0].ffn.w_down.dtype == torch.float32
+    assert torch.equal(e32.model.blocks[0].ffn.w_down, w.to(torch.float16).float())               # widened exactly
+    assert e16.model.blocks[0].ffn.w_down.dtype == torch.bfloat16                                 # matrices: the compute type
+    assert e16.model.final_norm.gain.dtype == torch.float32                                       # 16-bit float vectors are widened
+    assert torch.equal(e16.model.final_norm.gain, want.model.final_norm.gain.to(torch.float16).float())
+
+
+def test_make_random_model_command(tmp_path):
+    from llmengine_b200 import make_random_model
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(TINY_A))
+    assert make_random_model.main([str(cfg), str(tmp_path / "out"), "--seed", "9"]) == 0
+    ref = write_random_model(config_from_dict(TINY_A), 9, str(tmp_path / "ref"))
+    a = SafetensorsFile(str(tmp_path / "out" / "model.safetensors"))
+    b = SafetensorsFile(os.path.join(ref, "model.safetensors"))
+    assert all(torch.equal(a.tensor(n), b.tensor(n)) for n in b.names())
+    bad = tmp_path / "bad.json"
+    bad.write_text(json.dumps({"architectures": ["NoSuchModel"]}))
+    assert make_random_model.main([str(bad), str(tmp_path / "x")]) == 2

@@ -4,10 +4,14 @@ Some users of the kernel library cannot allocate device memory when they call it
 application that has handed the whole device to its own arenas and forbids cudaMalloc in the
 libraries it loads, or a serving loop that must not stall on an allocation.  For them the
 library keeps the scratch memory of the split-context decode attention in a device array of
-its own.  This test calls that entry point through its exported C symbol, twice in a row on
-different inputs (the second call finds the first call's partial results in the array), and
-checks each output against the regular entry point's, which works on a scratch buffer that
-the caller allocates.  It also checks that a call that would not fit the array is refused.
+its own.  This test calls that entry point through its exported C symbol, several times in a row on
+different inputs, and checks each output against the regular entry point's, which works on a
+scratch buffer that the caller allocates.  The first calls split each context over more blocks
+than one thread-block cluster holds, so the blocks' partial results and their ticket counters
+really pass through the built-in array, and the second call finds there what the first one left
+(partials of another batch shape; counters that must be back at zero).  A last call uses few
+splits, which merge inside a cluster and leave the array alone.  It also checks that a call that
+would not fit the array is refused.
 
 This file sorts last on purpose: a run that stops at the first failure has by then run every
 other test.
@@ -31,7 +35,7 @@ def test_static_scratch_entry_point_matches_the_regular_one():
     from llmengine_b200.kernels import build
     from llmengine_b200.kernels.ops import CudaOps, _FastAttnArgs
 
-    nh, nkv, hd, page, splits = 8, 2, 128, 16, 5
+    nh, nkv, hd, page = 8, 2, 128, 16
     ops = CudaOps(torch.device(DEV))
     path = build.ensure_built([f"attention_decode_static@HEAD_DIM={hd}"])[f"attention_decode_static@HEAD_DIM={hd}"]
     lib = ctypes.CDLL(path)
@@ -41,7 +45,8 @@ def test_static_scratch_entry_point_matches_the_regular_one():
     assert capacity == 1 << 20
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
-    for seed, ctx_lens in ((40, [700, 64, 5, 333]), (41, [129, 1000, 65])):      # two calls in a row
+    # more than 8 splits: merged through scratch memory by the block that finishes last; 5: inside a cluster
+    for seed, ctx_lens, splits in ((40, [700, 64, 5, 333], 12), (41, [129, 1000, 65], 16), (43, [900, 2, 257], 5)):
         case = _case(seed, ctx_lens, nh, nkv, hd, page)
         rows = torch.arange(len(ctx_lens), dtype=torch.int32, device=DEV)
         common = dict(q=case["q"], cache=case["cache"], rows=rows, cu_q_lens=case["cu_q_lens"],
