@@ -27,15 +27,16 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # that falls on the other side of a rounding step is carried on and amplified by a model with sharp
 # attention.  The yardstick is the model's own sensitivity to such rounding, measured on the plain
 # implementation: the distance between its bfloat16-rounded run and its 32-bit run.  The engine's distance
-# from the rounded plain run is the sum of the same kind of rounding steps, so it may be as large as that
-# yardstick (and 1e-2 at least); a key that is skipped, masked wrongly or read from a wrong page moves the
-# logits of the sharpened models by several times more.  (Measured: 0.3 to 0.6 of the yardstick.)
+# from the rounded plain run is the sum of the same kind of rounding steps: measured, it is 0.2 to 0.6 of
+# that yardstick for every configuration and schedule (the tests print it), so the bound is three quarters
+# of the yardstick (and 5e-3 at least).  The negative controls below show what the bound catches: one page
+# exchanged with another's moves the logits to 20 to 30 times the bound (10,000 times in 32-bit).
 TOL_F32 = 1e-4
 
 
 def bf16_tolerance(ref16, ref32):
     inherent = max(float((ref16[r] - ref32[r]).abs().max()) for r in ref16)
-    return max(1e-2, inherent)
+    return max(5e-3, 0.75 * inherent)
 
 
 CONFIGS = {
@@ -279,7 +280,7 @@ def test_logits_of_captured_decode_steps(tmp_path, monkeypatch, name, dtype, sho
     assert eng._graphs, "no decode step was captured"
     assert {k[1] for k in eng._graphs} == ({True, False} if short_context == 48 else {False})
     # two requests side by side, one token a step from the first token on
-    ids = {r: reqs[r] for r in list(reqs)[:2]}
+    ids = {r: reqs[r] for r in sorted(reqs, key=lambda r: -len(reqs[r]))[:2]}
     n = max(len(v) for v in ids.values())
     side = []
     for i in range(n):
