@@ -30,6 +30,7 @@ SOURCES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "gemm_skinny": "gemm_skinny.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
+    "utility": "utility.cu",
     # compiled per head size: ask for "attention_fast@HEAD_DIM=128"
     "attention_fast": "attention_fast.cu",
     # the tcgen05 portion kernel, per head size (64 or 128): "attention_tc@HEAD_DIM=128"

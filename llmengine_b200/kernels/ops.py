@@ -451,6 +451,26 @@ class CudaOps:
         """0 if no bounded wait of the tcgen05 kernels ever gave up (synchronises the device)."""
         return int(self._lib("gemm_tcgen05").llme_gemm_tc_status())
 
+    def random_fill(self, out: torch.Tensor, key: int, start: int, scale: float, offset: float,
+                    round_bf16_first: bool = False) -> torch.Tensor:
+        """out.flatten()[i] = offset + scale * z(key, start + i): the device twin of weights.loader.counter_normal."""
+        lib = self._lib("utility")
+        assert out.is_contiguous()
+        from ctypes import c_ulonglong
+        rc = lib.llme_random_fill(c_void_p(out.data_ptr()), c_int(_code(out.dtype)), c_ulonglong(key & ((1 << 64) - 1)),
+                                  c_longlong(start), c_longlong(out.numel()), c_float(scale), c_float(offset),
+                                  c_int(1 if round_bf16_first else 0), self._stream())
+        self._check(lib, rc, "random_fill")
+        return out
+
+    def read_stream(self, data: torch.Tensor, sink: torch.Tensor, blocks_per_sm: int = 4) -> None:
+        """Reads `data` once and stores nothing: what the memory delivers to a kernel that only loads."""
+        lib = self._lib("utility")
+        nbytes = data.numel() * data.element_size()
+        rc = lib.llme_read_stream(c_void_p(data.data_ptr()), c_longlong(nbytes), c_void_p(sink.data_ptr()),
+                                  c_int(blocks_per_sm), self._stream())
+        self._check(lib, rc, "read_stream")
+
     def repetition_penalty(self, logits, rows, tokens, counts, penalty) -> None:
         lib = self._lib("sampling")
         rc = lib.llme_repetition_penalty(c_void_p(logits.data_ptr()), c_longlong(logits.stride(0)),

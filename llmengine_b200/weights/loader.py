@@ -144,11 +144,20 @@ def random_model_weights(model, seed: int, compute: torch.dtype, device: torch.d
                          file_dtype: torch.dtype = torch.bfloat16) -> None:
     """Fill a model with random weights directly on the device (no folder is written): the tensors that
     `write_random_model` would store for the same seed, bit for bit.  Values pass through `file_dtype` as
-    they would through a file."""
+    they would through a file.  Where the kernel set has the generator (`random_fill`), every tensor is made
+    by one launch straight into its stored type."""
+    fill = getattr(model.rt.ops, "random_fill", None)
     tensors = {}
     for name, spec in model.weight_specs().items():
-        t = random_tensor(name, spec, seed, device).to(file_dtype)
-        tensors[name] = t.to(stored_dtype(spec, file_dtype, compute))
+        stored = stored_dtype(spec, file_dtype, compute)
+        if fill is not None and stored in (torch.float32, torch.bfloat16) and spec.init in ("normal", "gain"):
+            t = torch.empty(tuple(spec.shape), dtype=stored, device=device)
+            scale, offset = (0.02, 0.0) if spec.init == "normal" else (0.1, 1.0)
+            tensors[name] = fill(t, _tensor_seed(seed, name), 0, scale, offset,
+                                 round_bf16_first=file_dtype == torch.bfloat16 and stored != torch.bfloat16)
+        else:
+            t = random_tensor(name, spec, seed, device).to(file_dtype)
+            tensors[name] = t.to(stored)
     model.load_weights(tensors)
 
 

@@ -274,18 +274,19 @@ def test_logits_of_captured_decode_steps(tmp_path, monkeypatch, name, dtype, sho
     monkeypatch.setattr(Engine, "SHORT_CONTEXT", short_context)
     d, page, reqs, ref, tol = _setup(tmp_path, name, dtype, 2.0)
     steps = trace_bulk_then_single(reqs, 32)
-    eng = engine_for(d, dtype, max_live_tokens(steps, 64), page_size=page, use_cuda_graphs=True, max_model_len=256)
-    got = replay(eng, steps, poison=True)
-    compare(got, ref, tol, f"graphs/{name}/{dtype}/bulk_then_single")
-    assert eng._graphs, "no decode step was captured"
-    assert {k[1] for k in eng._graphs} == ({True, False} if short_context == 48 else {False})
-    # two requests side by side, one token a step from the first token on
     ids = {r: reqs[r] for r in sorted(reqs, key=lambda r: -len(reqs[r]))[:2]}
     n = max(len(v) for v in ids.values())
     side = []
     for i in range(n):
         entries = [(r, v[i:i + 1], [0]) for r, v in ids.items() if i < len(v)]
         side.append((entries, [r for r, v in ids.items() if i == len(v) - 1]))
+    pool = max(max_live_tokens(steps, 64), max_live_tokens(side, 64))
+    eng = engine_for(d, dtype, pool, page_size=page, use_cuda_graphs=True, max_model_len=256)
+    got = replay(eng, steps, poison=True)
+    compare(got, ref, tol, f"graphs/{name}/{dtype}/bulk_then_single")
+    assert eng._graphs, "no decode step was captured"
+    assert {k[1] for k in eng._graphs} == ({True, False} if short_context == 48 else {False})
+    # two requests side by side, one token a step from the first token on
     got = replay(eng, side, poison=True)
     compare(got, {r: ref[r] for r in ids}, tol, f"graphs/{name}/{dtype}/side by side")
     assert any(k[0] == 2 for k in eng._graphs)

@@ -230,3 +230,20 @@ def test_make_random_model_command(tmp_path):
     bad = tmp_path / "bad.json"
     bad.write_text(json.dumps({"architectures": ["NoSuchModel"]}))
     assert make_random_model.main([str(bad), str(tmp_path / "x")]) == 2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_random_weights_made_on_the_gpu_equal_the_written_folder(tmp_path, dtype):
+    """The device generator (one kernel launch per tensor) restates the host generator bit for bit."""
+    d = make_model_dir(str(tmp_path / "m"), TINY_B, 12)
+    ec = EngineConfig(dtype=dtype, max_cached_tokens=64, max_num_seqs=2, max_num_batched_tokens=64)
+    from_file = Engine(d, engine_config=ec)
+    from_seed = Engine(config=TINY_B, random_seed=12, engine_config=ec)
+    assert from_seed.ops.launches > 0
+    for a, b in zip(from_file.model.blocks, from_seed.model.blocks):
+        for x, y in ((a.mixer.w_qkv, b.mixer.w_qkv), (a.mixer.w_o, b.mixer.w_o), (a.ffn.w_gate_up, b.ffn.w_gate_up),
+                     (a.ffn.w_down, b.ffn.w_down), (a.mixer_norm.gain, b.mixer_norm.gain), (a.mixer.q_gain, b.mixer.q_gain)):
+            assert x.dtype == y.dtype and torch.equal(x, y)
+    assert torch.equal(from_file.model.head.weight, from_seed.model.head.weight)
+    assert torch.equal(from_file.model.embedding.table, from_seed.model.embedding.table)
