@@ -281,7 +281,7 @@ def test_logits_of_captured_decode_steps(tmp_path, monkeypatch, name, dtype, sho
         entries = [(r, v[i:i + 1], [0]) for r, v in ids.items() if i < len(v)]
         side.append((entries, [r for r, v in ids.items() if i == len(v) - 1]))
     pool = max(max_live_tokens(steps, 64), max_live_tokens(side, 64))
-    eng = engine_for(d, dtype, pool, page_size=page, use_cuda_graphs=True, max_model_len=256)
+    eng = engine_for(d, dtype, pool, page_size=page, use_cuda_graphs=True)
     got = replay(eng, steps, poison=True)
     compare(got, ref, tol, f"graphs/{name}/{dtype}/bulk_then_single")
     assert eng._graphs, "no decode step was captured"
