@@ -20,7 +20,6 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.base import PagedKVSpec, StateSpec
 
 
 class CacheError(RuntimeError):
@@ -112,7 +111,9 @@ class RequestState:
 class CacheManager:
     """Pages, block tables and state slots for up to `max_requests` live requests.
 
-    `specs[i] = (PagedKVSpec | StateSpec | None, cache_from)` for run i of the layer order.
+    `specs[i] = (cache spec | None, cache_from)` for run i of the layer order.  A cache spec is any object with
+    `paged`, `window`, `allocate(count, page_size, dtype, device)`, `bytes_per_token(dtype)` and, for states,
+    `zero_on_start` (parts/base.py describes them); the manager asks nothing else of it.
     """
 
     def __init__(self, specs: Sequence[Tuple[object, Optional[int]]], page_size: int, max_cached_tokens: int,
@@ -138,11 +139,11 @@ class CacheManager:
                                      f"{spec} differs from {self.specs[cache_from][0]}")
                 self.run_group.append(self.run_group[cache_from])
                 continue
-            if isinstance(spec, PagedKVSpec):
-                key = (page_size, spec.window)
+            if spec is not None and getattr(spec, "paged", False):
+                key = (page_size, int(getattr(spec, "window", 0)))
                 if key not in by_key:
                     by_key[key] = len(self.groups)
-                    self.groups.append(Group(page_size, spec.window, PagePool(num_pages), max_blocks=max_blocks))
+                    self.groups.append(Group(page_size, key[1], PagePool(num_pages), max_blocks=max_blocks))
                 self.groups[by_key[key]].runs.append(i)
                 self.run_group.append(by_key[key])
             else:
@@ -159,25 +160,24 @@ class CacheManager:
 
     # ------------------------------------------------------------------ device side
     def allocate_device(self, dtype: torch.dtype, device: torch.device) -> None:
-        """Make the page tensors [pages, 2, kv_heads, page_size, head_dim] of every owning paged run,
-        the state tensors [slots, *shape] of every stateful run, and the device block tables."""
+        """Make the page tensor of every owning paged run (for the attention of this package
+        [pages, 2, kv_heads, page_size, head_dim]), the state tensor [slots, ...] of every stateful run, each as
+        its spec lays it out, and the device block tables."""
         for i, (spec, cache_from) in enumerate(self.specs):
-            if cache_from is not None:
+            if cache_from is not None or spec is None:
                 continue
-            if isinstance(spec, PagedKVSpec):
+            if getattr(spec, "paged", False):
                 g = self.groups[self.run_group[i]]
-                self.kv[i] = torch.zeros(g.pool.num_pages, 2, spec.num_kv_heads, g.page_size, spec.head_dim,
-                                         dtype=dtype, device=device)
-            elif isinstance(spec, StateSpec):
-                self.state[i] = torch.zeros(self.max_requests, *spec.shape, dtype=spec.dtype, device=device)
+                self.kv[i] = spec.allocate(g.pool.num_pages, g.page_size, dtype, device)
+            else:
+                self.state[i] = spec.allocate(self.max_requests, self.page_size, dtype, device)
         self.tables_dev = [torch.from_numpy(t).to(device) for t in self.tables]
         self._patch_ring = [(None, None) for _ in range(8)]
         self._patch_next = 0
 
     def bytes_per_token(self, dtype: torch.dtype) -> int:
-        size = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * s.num_kv_heads * s.head_dim * size for s, c in self.specs
-                   if isinstance(s, PagedKVSpec) and c is None)
+        return sum(int(s.bytes_per_token(dtype)) for s, c in self.specs
+                   if s is not None and c is None and getattr(s, "paged", False))
 
     def flush(self) -> None:
         """Bring the device block tables and the states of newly started requests up to date, without
@@ -215,8 +215,9 @@ class CacheManager:
                 event.record()
             self.tables_dev[gi].view(-1).index_copy_(0, dev[0], dev[1].to(torch.int32))
         for slot in self._new_slots:
-            for st in self.state.values():
-                st[slot].zero_()
+            for run, st in self.state.items():
+                if getattr(self.specs[run][0], "zero_on_start", True):
+                    st[slot].zero_()
         self._new_slots = []
 
     # ------------------------------------------------------------------ requests

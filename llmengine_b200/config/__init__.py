@@ -87,7 +87,10 @@ class EngineConfig:
     max_model_len: int = 0               # 0 = the model's max_position_embeddings
     seed: int = 42                       # default sampling seed, as the reference's Sampler(42)
     use_cuda_graphs: bool = True         # capture decode-only steps
-    kernels: str = "fast"                # "fast" or "plain": which attention/GEMM kernels the bf16 path uses
+    # which kernels serve the operations: "fast", "plain" (the plain twins and the library product everywhere), or a
+    # mapping operation -> variant that exchanges single kernels inside the whole model, e.g.
+    # {"attention.portion": "mma", "linear": "cublas"} (the operations and their variants: executor.h)
+    kernels: Any = "fast"
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:
@@ -99,8 +102,8 @@ class EngineConfig:
             raise ConfigError(f"dtype must be bfloat16 or float32, got {self.dtype!r}")
         if self.page_size <= 0 or self.page_size > 256:
             raise ConfigError(f"page_size must be in 1..256, got {self.page_size}")
-        if self.kernels not in ("fast", "plain"):
-            raise ConfigError(f"kernels must be 'fast' or 'plain', got {self.kernels!r}")
+        if not (self.kernels in ("fast", "plain") or isinstance(self.kernels, Mapping)):
+            raise ConfigError(f"kernels must be 'fast', 'plain' or a mapping operation -> variant, got {self.kernels!r}")
         for k in ("max_num_seqs", "max_num_batched_tokens", "prefill_chunk"):
             if getattr(self, k) <= 0:
                 raise ConfigError(f"{k} must be positive")

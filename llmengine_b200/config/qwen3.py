@@ -254,7 +254,7 @@ class Qwen3Config:
             order=tuple(LayerRun(l, c) for l, c in self.layer_order),
             final_norm=norm,
             lm_head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
-                                         "tied": self.tie_word_embeddings}),
+                                         "tied_to": "model.embed_tokens.weight" if self.tie_word_embeddings else None}),
             embedding_prefix="model.embed_tokens", final_norm_prefix="model.norm", lm_head_prefix="lm_head",
         )
         spec.validate()

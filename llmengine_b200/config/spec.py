@@ -30,18 +30,34 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement and the four parts it arranges.
+    """One layer: a block arrangement and the parts it arranges, by role.
 
-    `prefix` is the layer's tensor-name prefix in the weight file; the parts'
+    `parts` maps a role name to a part; which roles exist is the block kind's business (the pre-norm residual
+    block reads "mixer", "mixer_norm", "feed_forward" and "feed_forward_norm"; a block with a post-norm, one
+    shared norm for parallel branches or no feed-forward names its own).  The four keyword arguments are a
+    shorthand for those four roles.  `prefix` is the layer's tensor-name prefix in the weight file; the parts'
     own tensor names are appended to it by the block.
     """
 
     prefix: str
     block: PartSpec
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    mixer: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
+    parts: Mapping[str, PartSpec] = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        merged = dict(self.parts)
+        for role in ("mixer", "mixer_norm", "feed_forward", "feed_forward_norm"):
+            given = getattr(self, role)
+            if given is not None:
+                if role in merged and merged[role] != given:
+                    raise ValueError(f"layer {self.prefix!r}: the part {role!r} is given twice")
+                merged[role] = given
+            elif role in merged:
+                object.__setattr__(self, role, merged[role])
+        object.__setattr__(self, "parts", merged)
 
 
 @dataclass(frozen=True)

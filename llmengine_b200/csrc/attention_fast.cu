@@ -77,6 +77,8 @@ struct FusedQkv {
     int max_positions;
     int write_kv;                // 0: the layer reads another layer's cache and stores nothing
 };
+#include "kernel_args.h"
+static_assert(sizeof(FastAttnArgs) == sizeof(LlmeFastAttnArgs) && sizeof(FusedQkv) == sizeof(LlmeFusedQkv), "the argument blocks must match kernel_args.h");
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 

@@ -25,6 +25,8 @@ struct AttnArgs {
     int window;                 // 0 = all keys up to the query; W > 0 = the last W of them
     float scale;
 };
+#include "kernel_args.h"
+static_assert(sizeof(AttnArgs) == sizeof(LlmeAttnArgs), "the argument block must match kernel_args.h");
 
 template <typename T, int REGS>
 __global__ void attention_plain_kernel(AttnArgs a) {

@@ -81,6 +81,8 @@ struct TcAttnArgs {
     int max_blocks, n_rows, nh, nkv, page_size, window;
     float scale;
 };
+#include "kernel_args.h"
+static_assert(sizeof(TcAttnArgs) == sizeof(LlmeTcAttnArgs), "the argument block must match kernel_args.h");
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {

@@ -241,6 +241,8 @@ struct QkvArgs {
     void* cache; const int* slot_mapping;         // nullable
     int tokens, nh, nkv, hd, page_size;
 };
+#include "kernel_args.h"
+static_assert(sizeof(QkvArgs) == sizeof(LlmeQkvArgs), "the argument block must match kernel_args.h");
 
 template <typename I, typename O, typename G>
 __global__ void qkv_post_kernel(QkvArgs a) {

@@ -45,6 +45,18 @@ class StepBatch:
     portion_rows: torch.Tensor      # int32 [NP] batch rows of the other requests
     groups: List[GroupView] = field(default_factory=list)
     assume_ctx: Optional[int] = None   # set when the step is (to be) captured: size launches for this context length
+    logits: Optional[torch.Tensor] = None   # [NL, vocab] 32-bit: where the step's logits go
+
+    @classmethod
+    def bare(cls, num_tokens: int, device, token_ids: Optional[torch.Tensor] = None,
+             logit_rows: Optional[torch.Tensor] = None, logits: Optional[torch.Tensor] = None) -> "StepBatch":
+        """A step without requests or caches: `num_tokens` rows for operations that need nothing else
+        (a part that is run by itself)."""
+        e = torch.zeros(0, dtype=torch.int32, device=device)
+        return cls(num_tokens=num_tokens, num_requests=0, q_lens=[], start_positions=[],
+                   token_ids=token_ids if token_ids is not None else e, positions=e, token_request=e, cu_q_lens=e,
+                   ctx_lens=e, state_slots=e, first_portion=e, logit_rows=logit_rows if logit_rows is not None else e,
+                   decode_rows=e, portion_rows=e, groups=[], logits=logits)
 
     @property
     def max_q_len(self) -> int:
@@ -69,17 +81,4 @@ class StepBatch:
         return all(q == 1 for q in self.q_lens)
 
 
-@dataclass
-class PagedKVView:
-    """The cache a paged mixer run works on."""
-
-    kv: torch.Tensor                # [pages, 2, kv_heads, page_size, head_dim]
-    group: int                      # index into StepBatch.groups
-    writes: bool                    # False when the run reads another run's cache
-
-
-@dataclass
-class StateView:
-    """The fixed-size states of a stateful mixer run: row `batch.state_slots[r]` belongs to request r."""
-
-    state: torch.Tensor             # [slots, *shape]
+from ..parts.base import PagedKVView, StateView  # noqa: E402,F401  (their home is beside the cache specs)

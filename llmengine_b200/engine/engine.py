@@ -22,9 +22,9 @@ import torch
 
 from ..cache import CacheError, CacheManager, OutOfPages
 from ..config import EngineConfig, config_from_dict, load_config
-from ..parts.base import PagedKVSpec, Runtime, StateSpec
+from ..parts.base import Runtime
 from ..weights import load_model_weights, random_model_weights
-from .batch import GroupView, PagedKVView, StateView, StepBatch
+from .batch import GroupView, StepBatch
 from .model import Model
 
 
@@ -65,9 +65,9 @@ class Engine:
         self.ops = ops
         self.spec = self.config.model_spec()
         self.max_model_len = min(ec.max_model_len or self.spec.max_positions, self.spec.max_positions)
-        if hasattr(ops, "use_tcgen05"):
-            ops.use_tcgen05 = ec.kernels == "fast"
-        self.rt = Runtime(ops, self.device, self.dtype, ec.max_num_batched_tokens, ec.kernels)
+        if hasattr(ops, "choose_kernels"):
+            ops.choose_kernels(ec.kernels)
+        self.rt = Runtime(ops, self.device, self.dtype, ec.max_num_batched_tokens, ec.kernels, ec.max_num_seqs)
         self.model = Model(self.spec, self.rt)
         if model_dir is not None:
             load_model_weights(self.model, self.config, model_dir, self.dtype, self.device)
@@ -84,28 +84,24 @@ class Engine:
         self._caches = []
         for i, (spec, cache_from) in enumerate(specs):
             owner = self.cache.run_owner[i]
-            if isinstance(spec, PagedKVSpec):
-                self._caches.append(PagedKVView(self.cache.kv[owner], self.cache.run_group[i], cache_from is None))
-            elif isinstance(spec, StateSpec):
-                self._caches.append(StateView(self.cache.state[owner]))
-            else:
+            if spec is None:
                 self._caches.append(None)
+                continue
+            tensor = self.cache.kv[owner] if getattr(spec, "paged", False) else self.cache.state[owner]
+            self._caches.append(spec.view(tensor, self.cache.run_group[i], cache_from is None))
         self._init_metadata()
         self.steps = 0
         # decode-only steps are captured in CUDA graphs, one per batch size, after one eager step of that size
         self.graphs_enabled = (bool(ec.use_cuda_graphs) and self.device.type == "cuda"
-                               and all(p.capture_safe for p in self.model.parts()))
+                               and all(p.capture_safe and hasattr(p, "emit") for p in self.model.parts()))
         self._graphs: Dict[tuple, tuple] = {}
         self._graph_seen: set = set()
         self._graph_pool = None
 
     # ------------------------------------------------------------------ sizing
     def _tokens_from_free_memory(self, specs) -> int:
-        per_token = 0
-        size = 2 if self.dtype == torch.bfloat16 else 4
-        for s, c in specs:
-            if isinstance(s, PagedKVSpec) and c is None:
-                per_token += 2 * s.num_kv_heads * s.head_dim * size
+        per_token = sum(int(s.bytes_per_token(self.dtype)) for s, c in specs
+                        if s is not None and c is None and getattr(s, "paged", False))
         if per_token == 0:
             return self.ec.page_size
         if self.device.type != "cuda":

@@ -31,6 +31,8 @@ SOURCES: Dict[str, str] = {
     "gemm_skinny": "gemm_skinny.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "utility": "utility.cu",
+    # the step executor (host code): walks a model's plan and launches the kernels of the other libraries
+    "executor": "executor.cu",
     # compiled per head size: ask for "attention_fast@HEAD_DIM=128"
     "attention_fast": "attention_fast.cu",
     # the tcgen05 portion kernel, per head size (64 or 128): "attention_tc@HEAD_DIM=128"
@@ -48,6 +50,11 @@ VARIANTS: Dict[str, List[str]] = {
     "attention_decode_static": ["attention_decode_static@HEAD_DIM=128"],
     "attention_tc": ["attention_tc@HEAD_DIM=64", "attention_tc@HEAD_DIM=128"],
 }
+
+INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
+
+# link flags of single libraries
+LINK: Dict[str, List[str]] = {"executor": ["-ldl"]}
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -107,6 +114,11 @@ def _digest(key: str) -> str:
             with open(os.path.join(CSRC, fn), "rb") as f:
                 h.update(fn.encode())
                 h.update(f.read())
+    for root, _dirs, files in sorted(os.walk(INCLUDE)):
+        for fn in sorted(files):
+            with open(os.path.join(root, fn), "rb") as f:
+                h.update(fn.encode())
+                h.update(f.read())
     return h.hexdigest()[:12]
 
 
@@ -129,7 +141,8 @@ def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) 
     for n in todo:
         tmp = f"{paths[n]}.{os.getpid()}.tmp"
         name, defines = split_key(n)
-        cmd = [nvcc, *NVCC_FLAGS, *defines, *(extra_flags or []), "-I", CSRC, "-o", tmp, os.path.join(CSRC, SOURCES[name])]
+        cmd = [nvcc, *NVCC_FLAGS, *defines, *(extra_flags or []), "-I", CSRC, "-I", INCLUDE, "-o", tmp,
+               os.path.join(CSRC, SOURCES[name]), *LINK.get(name, [])]
         _log(f"compiling {SOURCES[name]} {' '.join(defines)} for sm_100a ...".replace("  ", " "))
         log = tempfile.TemporaryFile(mode="w+")          # not a pipe: a long error listing must not block nvcc
         procs[n] = (subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT, text=True), tmp, log)

@@ -2,11 +2,16 @@
 their `extern "C"` entry points on torch tensors, on torch's current stream.
 
 There is no fallback: without a CUDA device, or if a library cannot be compiled
-or loaded, `CudaOps` raises `KernelsUnavailable`.  The only library matrix
-product is the bfloat16 `linear`, which goes to cuBLAS through `torch.mm` (the
-reference also hands its dense products to cuBLAS:
-src/runtime/kernels/cuda_kernels.cu:892-908); the 32-bit `linear` runs this
-package's own FMA kernel.
+or loaded, `CudaOps` raises `KernelsUnavailable`.
+
+A model does not call these methods one by one: its parts emit a plan once (engine/plan.py), `compile` turns
+it into the records of the native executor (csrc/executor.cu, include/llmengine_b200/executor.h), and every
+step is one call that walks them in C++.  Which kernel serves an operation for a step's shape is decided there,
+in one place; `choose` exchanges single kernels (`EngineConfig.kernels`).  The only library matrix product is the
+bfloat16 product of 17 to 127 tokens (and of larger steps whose tiles would not fill the GPU), which goes to
+cuBLAS (the reference also hands its dense products to cuBLAS: src/runtime/kernels/cuda_kernels.cu:892-908);
+the 32-bit product is this package's own FMA kernel.  The methods below that launch one kernel directly are what
+the kernel tests and tools use.
 """
 from __future__ import annotations
 
@@ -18,6 +23,7 @@ from typing import Dict, Optional
 import torch
 
 from . import build
+from . import executor as ex
 
 
 class KernelsUnavailable(RuntimeError):
@@ -109,12 +115,123 @@ class CudaOps:
             raise KernelsUnavailable(f"device {device} is not a CUDA device")
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._libs: Dict[str, ctypes.CDLL] = {}
-        self.use_tcgen05 = True    # products of 128 tokens or more on this package's tcgen05 kernel, else cuBLAS
-        self.plain_gemm = os.environ.get("LLME_GEMM", "auto")   # "auto" | "tcgen05" | "cublas", see _tc_fills_its_waves
-        if self.plain_gemm not in ("auto", "tcgen05", "cublas"):
-            raise KernelError(f"LLME_GEMM must be auto, tcgen05 or cublas, got {self.plain_gemm!r}")
         self._sms = None
-        self.launches = 0          # kernels of this package launched so far (cuBLAS calls are not counted)
+        self._direct = 0           # kernels launched through the methods below (the executor counts its own)
+        self._xlib = self._lib("executor")
+        ex.declare(self._xlib)
+        with torch.cuda.device(self.device):
+            self._ex = self._xlib.llme_executor_create(self._device_index)
+        if not self._ex:
+            raise KernelsUnavailable(f"the step executor cannot use device {device}")
+
+    def __del__(self):
+        try:
+            if getattr(self, "_ex", None):
+                self._xlib.llme_executor_destroy(self._ex)
+                self._ex = None
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ the executor
+    @property
+    def launches(self) -> int:
+        """Kernels of this package launched so far (library products are not counted)."""
+        return self._direct + int(self._xlib.llme_executor_launches(self._ex))
+
+    @launches.setter
+    def launches(self, value: int) -> None:
+        self._direct = int(value) - int(self._xlib.llme_executor_launches(self._ex))
+
+    def choose(self, op: str, variant: str) -> None:
+        """Which implementation an operation takes from now on (operations and variants: executor.h)."""
+        if self._xlib.llme_executor_choose(self._ex, op.encode(), variant.encode()) != 0:
+            raise KernelError(self._xlib.llme_executor_error(self._ex).decode())
+
+    def chosen(self, op: str) -> str:
+        return self._xlib.llme_executor_chosen(self._ex, op.encode()).decode()
+
+    def choose_kernels(self, kernels) -> None:
+        """`EngineConfig.kernels`: "fast", "plain", or a mapping operation -> variant applied on top of "fast"."""
+        if isinstance(kernels, str):
+            self.choose("*", kernels)
+            return
+        self.choose("*", "fast")
+        for op, variant in dict(kernels).items():
+            self.choose(op, variant)
+
+    @property
+    def plain_gemm(self) -> str:
+        return self.chosen("linear")
+
+    @plain_gemm.setter
+    def plain_gemm(self, variant: str) -> None:
+        self.choose("linear", variant)
+
+    def attention_scratch_floats(self, max_requests: int, num_heads: int, num_kv_heads: int, head_dim: int) -> int:
+        return int(self._xlib.llme_attention_scratch_floats(self._ex, max_requests, num_heads, num_kv_heads, head_dim))
+
+    def decode_splits(self, requests: int, num_heads: int, num_kv_heads: int, window: int, max_ctx: int) -> int:
+        return int(self._xlib.llme_decode_splits(self._ex, requests, num_heads, num_kv_heads, window, max_ctx))
+
+    _ENTRY_POINTS = {
+        "elementwise": {"embedding": "llme_embedding", "rmsnorm": "llme_rmsnorm", "qkv_post": "llme_qkv_post",
+                        "swiglu": "llme_swiglu"},
+        "gemm_f32": {"gemm_f32": "llme_gemm_nt_f32"},
+        "gemm_skinny": {"gemm_skinny": "llme_gemm_skinny_bf16", "gemm_skinny_swiglu": "llme_gemm_skinny_swiglu_bf16"},
+        "gemm_tcgen05": {"gemm_tc": "llme_gemm_tc_bf16", "gemm_tc_swiglu": "llme_gemm_tc_swiglu_bf16"},
+        "attention_plain": {"attention_plain": "llme_attention_plain"},
+        "attention_fast": {"attention_portion/{hd}": "llme_attention_portion", "attention_decode/{hd}": "llme_attention_decode",
+                           "attention_decode_fused/{hd}": "llme_attention_decode_fused",
+                           "attention_decode_scratch/{hd}": "llme_attention_decode_scratch_floats"},
+        "attention_tc": {"attention_tc/{hd}": "llme_attention_tc"},
+    }
+
+    def _register(self, key: str, lib: ctypes.CDLL) -> None:
+        """Hand a kernel library's entry points (and its error text) to the executor, by name."""
+        name, _, rest = key.partition("@")
+        hd = rest.partition("=")[2]
+        for entry, symbol in self._ENTRY_POINTS.get(name, {}).items():
+            entry = entry.format(hd=hd)
+            fn = ctypes.cast(getattr(lib, symbol), c_void_p)
+            self._xlib.llme_executor_register(self._ex, entry.encode(), fn)
+            self._xlib.llme_executor_register(self._ex, f"error/{entry.split('/')[0]}".encode(),
+                                              ctypes.cast(lib.llme_last_error, c_void_p))
+
+    def _libraries_for(self, plan) -> list:
+        """The kernel libraries a plan can reach with the present choices: what has to be compiled for this model."""
+        need = []
+
+        def want(n):
+            if n not in need:
+                need.append(n)
+        fast_attention = self.chosen("attention") == "fast"
+        for op in plan.ops:
+            a = op.a
+            if op.kind in ("embedding", "rmsnorm", "qkv_post", "attention"):
+                want("elementwise")
+            if op.kind in ("linear", "linear_swiglu"):
+                if a["x"].dtype == torch.float32:
+                    want("gemm_f32")
+                elif self.chosen("linear") != "plain":
+                    want("gemm_skinny")
+                    if self.chosen("linear") != "cublas":
+                        want("gemm_tcgen05")
+                if op.kind == "linear_swiglu":
+                    want("elementwise")
+            if op.kind in ("attend", "attention"):
+                hd, dt = a["head_dim"], a["q"].dtype
+                if fast_attention and self.fast_attention_supports(hd, dt):
+                    want(f"attention_fast@HEAD_DIM={hd}")
+                    if hd in (64, 128) and self.chosen("attention.portion") == "tcgen05":
+                        want(f"attention_tc@HEAD_DIM={hd}")
+                else:
+                    want("attention_plain")
+        return need
+
+    def compile(self, plan) -> "CompiledPlan":
+        """The native records of a plan, ready to run step after step."""
+        self.require(*self._libraries_for(plan))
+        return CompiledPlan(self, plan)
 
     # ------------------------------------------------------------------ loading
     def require(self, *names: str) -> None:
@@ -133,6 +250,8 @@ class CudaOps:
                 raise KernelsUnavailable(f"cannot load {paths[n]}: {e}") from None
             lib.llme_last_error.restype = c_char_p
             self._libs[n] = lib
+            if n != "executor" and getattr(self, "_ex", None):
+                self._register(n, lib)
 
     def _lib(self, name: str) -> ctypes.CDLL:
         lib = self._libs.get(name)
@@ -142,7 +261,7 @@ class CudaOps:
         return lib
 
     def _check(self, lib: ctypes.CDLL, rc: int, what: str) -> None:
-        self.launches += 1
+        self._direct += 1
         if rc != 0:
             msg = lib.llme_last_error().decode("utf-8", "replace")
             raise KernelError(f"{what}: {msg} (code {rc})")
@@ -253,7 +372,7 @@ class CudaOps:
                               page_size: int) -> bool:
         """Whether the tcgen05 portion kernel takes this shape (head size 64 or 128, pages of 8..128 that
         divide 128 or multiples of 128, a group size that divides 128)."""
-        if not (self.use_tcgen05 and dtype == torch.bfloat16 and head_dim in (64, 128)):
+        if not (dtype == torch.bfloat16 and head_dim in (64, 128)):
             return False
         g = num_heads // num_kv_heads
         pages_ok = page_size >= 8 and (128 % page_size == 0 if page_size <= 128 else page_size % 128 == 0)
@@ -326,113 +445,43 @@ class CudaOps:
         self._check(lib, rc, "swiglu")
         return out
 
+    def _run_one(self, record) -> None:
+        """One operation through the executor, for all rows of its input (what `linear` and `linear_swiglu` below do):
+        the executor's choice of kernel, outside any model."""
+        from ..engine.batch import StepBatch
+        from ..engine.plan import Plan
+        plan = Plan()
+        record(plan)
+        rows = plan.ops[0].a["x"].shape[0]
+        if rows > 0:
+            self.compile(plan).run(StepBatch.bare(rows, self.device))
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        """out[M,N] = x[M,K] @ w[N,K]^T.  32-bit operands: this package's FMA kernel (never a
-        reduced-precision mode).  bfloat16 operands: cuBLAS with 32-bit accumulation, the output
-        in `out`'s type."""
-        M, K = x.shape
-        N = w.shape[0]
-        assert w.shape[1] == K and out.shape == (M, N)
-        if x.dtype == torch.float32:
-            lib = self._lib("gemm_f32")
-            assert out.dtype == torch.float32 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-            rc = lib.llme_gemm_nt_f32(c_void_p(x.data_ptr()), c_void_p(w.data_ptr()), c_int(_code(w.dtype)),
-                                      c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
-                                      c_longlong(x.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                                      self._stream())
-            self._check(lib, rc, "gemm_f32")
-            return out
-        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-        if M == 0:
-            return out
-        if self.skinny_supports(x, w, out):
-            # a handful of tokens: this package's weight-streaming kernel
-            lib = self._lib("gemm_skinny")
-            rc = lib.llme_gemm_skinny_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w.data_ptr()),
-                                           c_longlong(w.stride(0)), c_void_p(out.data_ptr()), c_int(_code(out.dtype)),
-                                           c_longlong(out.stride(0)), c_int(M), c_int(N), c_int(K), self._stream())
-            self._check(lib, rc, "gemm_skinny")
-            return out
-        if (self.use_tcgen05 and M >= 128 and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-                and self._tc_fills_its_waves(M, N)):
-            # many tokens: this package's tcgen05 kernel (TMA-fed, accumulator in tensor memory)
-            return self.linear_tc(x, w, out)
-        if out.dtype == torch.bfloat16:
-            # torch lets cuBLAS add partial sums in bfloat16 unless told otherwise, and for some shapes (a few
-            # tokens, an odd width) cuBLAS then does: results a thousand rounding steps off.  Not here.
-            mm = torch.backends.cuda.matmul
-            keep = mm.allow_bf16_reduced_precision_reduction
-            mm.allow_bf16_reduced_precision_reduction = False
-            try:
-                torch.mm(x, w.t(), out=out)
-            finally:
-                mm.allow_bf16_reduced_precision_reduction = keep
-        else:
-            torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+        """out[M,N] = x[M,K] @ w[N,K]^T by the kernel the executor chooses for this shape.  32-bit operands: this
+        package's FMA kernel (never a reduced-precision mode).  bfloat16 operands: the weight-streaming kernel for
+        up to 16 rows, the tcgen05 kernel for 128 rows or more when its tiles fill the GPU, else cuBLAS with 32-bit
+        accumulation; the output in `out`'s type."""
+        assert w.shape[1] == x.shape[1] and out.shape == (x.shape[0], w.shape[0])
+        self._run_one(lambda plan: plan.linear(x, w, out))
         return out
 
-    def _tc_fills_its_waves(self, M: int, N: int) -> bool:
-        """Whether a plain product of this size goes to this package's tcgen05 kernel rather than to cuBLAS.
-
-        The kernel walks over whole 128 x 256 tiles, one block per SM: 256 tiles on 148 SMs take the time of two
-        waves for 1.73 waves of work, and there cuBLAS, which balances such a product, is 10-15 % faster (measured
-        for 2,048 tokens: 70/50/136 us against 81/58/158 us for the q|k|v, output and down products of the 8B
-        shape).  `plain_gemm` = "tcgen05" or "cublas" (or LLME_GEMM in the environment) forces one of them;
-        "auto" takes the kernel when its last wave is at least 90 % full."""
-        if self.plain_gemm != "auto":
-            return self.plain_gemm == "tcgen05"
-        tiles = -(-M // 128) * -(-N // (256 if N > 128 else 128))
-        sms = self._sm_count()
-        waves = -(-tiles // sms)
-        return tiles >= 0.9 * waves * sms
-
-    def _sm_count(self) -> int:
-        if self._sms is None:
-            self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        return self._sms
-
-    def skinny_supports(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-        """Whether the weight-streaming kernel for a handful of tokens takes this product."""
-        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= 16 and x.shape[1] % 8 == 0
-                and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1 and x.stride(0) % 8 == 0
-                and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-    def _tc_swiglu_supports(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-        # its tile is 128 tokens x (128 gate + 128 up) rows; like the plain product it is taken only when its last
-        # wave is nearly full (2,048 tokens of the 8B shape: 289 us against 287 us for cuBLAS and a SwiGLU kernel
-        # behind it; 256 / 512 / 1,024 tokens: 83 / 106 / 172 us against 69 / 85 / 150 us)
-        return (self.use_tcgen05 and x.dtype == w.dtype == out.dtype == torch.bfloat16 and x.shape[0] >= 128
-                and self._tc_fills_its_waves(x.shape[0], 2 * out.shape[1])
-                and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and out.shape[1] >= 8
-                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
-
     def linear_swiglu_supports(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
-        """Whether linear_swiglu() takes this product: a handful of tokens (the weight-streaming kernel) or at
-        least 128 of them (the tcgen05 kernel), bfloat16."""
-        return self.skinny_supports(x, w_gate_up, out) or self._tc_swiglu_supports(x, w_gate_up, out)
+        """Whether a kernel with the activation in its epilogue exists for this product (a handful of rows: the
+        weight-streaming kernel; 128 rows or more: the tcgen05 kernel; bfloat16, 16-byte aligned rows)."""
+        M, K = x.shape
+        return (x.dtype == w_gate_up.dtype == out.dtype == torch.bfloat16 and (0 < M <= 16 or M >= 128) and K % 8 == 0
+                and x.stride(1) == 1 and w_gate_up.stride(1) == 1 and out.stride(1) == 1 and x.stride(0) % 8 == 0
+                and w_gate_up.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and out.shape[1] >= 8
+                and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
     def linear_swiglu(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        """out[M, I] = silu(x @ Wg^T) * (x @ Wu^T) with w_gate_up = [Wg | Wu] stacked by rows, in one kernel;
-        only where linear_swiglu_supports() holds."""
+        """out[M, I] = silu(x @ Wg^T) * (x @ Wu^T) with w_gate_up = [Wg | Wu] stacked by rows: in one kernel where the
+        executor has one for the shape, else the product and the activation kernel behind it."""
         M, K = x.shape
         inter = out.shape[1]
         assert w_gate_up.shape == (2 * inter, K) and out.shape[0] == M
-        if self.skinny_supports(x, w_gate_up, out):
-            lib = self._lib("gemm_skinny")
-            rc = lib.llme_gemm_skinny_swiglu_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w_gate_up.data_ptr()),
-                                                  c_longlong(w_gate_up.stride(0)), c_void_p(out.data_ptr()),
-                                                  c_int(_code(out.dtype)), c_longlong(out.stride(0)), c_int(M), c_int(inter),
-                                                  c_int(K), self._stream())
-            self._check(lib, rc, "gemm_skinny_swiglu")
-            return out
-        assert self._tc_swiglu_supports(x, w_gate_up, out)
-        lib = self._lib("gemm_tcgen05")
-        rc = lib.llme_gemm_tc_swiglu_bf16(c_void_p(x.data_ptr()), c_longlong(x.stride(0)), c_void_p(w_gate_up.data_ptr()),
-                                          c_longlong(w_gate_up.stride(0)), c_void_p(out.data_ptr()), c_longlong(out.stride(0)),
-                                          c_int(M), c_int(inter), c_int(K), self._stream())
-        self._check(lib, rc, "gemm_tcgen05_swiglu")
+        gate_up = torch.empty(M, 2 * inter, dtype=x.dtype, device=x.device)
+        self._run_one(lambda plan: plan.linear_swiglu(x, w_gate_up, gate_up, out))
         return out
 
     def linear_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -487,3 +536,72 @@ class CudaOps:
         rc = lib.llme_sample(byref(a), self._stream())
         self._check(lib, rc, "sample")
         return out
+
+
+class CompiledPlan:
+    """A plan as the native executor holds it.  `run(batch)` is one call into C++ that launches the whole step on
+    torch's current stream."""
+
+    def __init__(self, ops: CudaOps, plan) -> None:
+        self.ops = ops
+        self._lib = ops._xlib
+        self._keep: list = [plan]
+        self._handle = self._lib.llme_plan_create(ops._ex)
+        self._failure: Optional[BaseException] = None
+        self._step = ex.Step()
+        for i, op in enumerate(plan.ops):
+            if op.kind == "call":
+                fn = ex.CallFn(self._guard(op.a["fn"]))
+                self._keep.append(fn)
+                kind, rec = ex.OP_CALL, ex.CallOp(fn, None)
+            else:
+                kind, rec = ex.records(op, self._keep)
+            if self._lib.llme_plan_add(self._handle, kind, byref(rec), ctypes.sizeof(rec)) < 0:
+                raise KernelError(f"operation {i} ({op.kind}): {self._lib.llme_executor_error(ops._ex).decode()}")
+
+    def __del__(self):
+        try:
+            if self._handle:
+                self._lib.llme_plan_destroy(self._handle)
+                self._handle = None
+        except Exception:
+            pass
+
+    def _guard(self, fn):
+        """A part that runs in Python inside the native walk: its exception is kept and raised after the walk."""
+        def call(_user, _step, _stream):
+            try:
+                fn(self._batch)
+                return 0
+            except BaseException as e:          # noqa: BLE001  (re-raised by run)
+                self._failure = e
+                return -2
+        return call
+
+    def run(self, batch, first: int = 0, count: int = -1) -> None:
+        s = self._step
+        s.num_tokens, s.num_requests = batch.num_tokens, batch.num_requests
+        s.num_logit_rows = batch.logit_rows.numel()
+        s.num_decode, s.num_portion = batch.decode_rows.numel(), batch.portion_rows.numel()
+        s.max_portion_len, s.max_decode_ctx = batch.max_portion_len, batch.max_decode_ctx
+        s.token_ids, s.positions, s.token_request = batch.token_ids.data_ptr(), batch.positions.data_ptr(), batch.token_request.data_ptr()
+        s.cu_q_lens, s.ctx_lens, s.state_slots = batch.cu_q_lens.data_ptr(), batch.ctx_lens.data_ptr(), batch.state_slots.data_ptr()
+        s.first_portion, s.logit_rows = batch.first_portion.data_ptr(), batch.logit_rows.data_ptr()
+        s.decode_rows, s.portion_rows = batch.decode_rows.data_ptr(), batch.portion_rows.data_ptr()
+        s.logits = batch.logits.data_ptr() if batch.logits is not None else None
+        s.blas = torch.cuda.current_blas_handle()
+        if len(batch.groups) > ex.MAX_GROUPS:
+            raise KernelError(f"a step has {len(batch.groups)} cache groups, the executor takes {ex.MAX_GROUPS}")
+        s.num_groups = len(batch.groups)
+        for i, g in enumerate(batch.groups):
+            sg = s.groups[i]
+            sg.block_tables, sg.slot_mapping = g.block_tables.data_ptr(), g.slot_mapping.data_ptr()
+            sg.max_blocks, sg.page_size, sg.window = g.block_tables.shape[1], g.page_size, g.window
+        self._batch = batch
+        rc = self._lib.llme_plan_run(self._handle, byref(s), first, count, self.ops._stream())
+        self._batch = None
+        if rc != 0:
+            failure, self._failure = self._failure, None
+            if failure is not None:
+                raise failure
+            raise KernelError(self._lib.llme_executor_error(self.ops._ex).decode())

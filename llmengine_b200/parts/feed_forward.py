@@ -5,14 +5,16 @@ from typing import Dict
 
 import torch
 
-from .base import Part, Runtime, WeightSpec, register_part
+from ..engine.plan import Plan
+from .base import Part, Runtime, WeightSpec, register_part, run_alone
 
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
     """down( silu(gate(h)) * up(h) ), no biases; silu(g) = g / (1 + exp(-g))
     (src/model/transformer_graph_builder.cpp:261-274; src/runtime/kernels/cpu_kernels.cpp:848-859).
-    The gate and up matrices are stored as one [gate | up] matrix so that one product serves both."""
+    The gate and up matrices are stored as one [gate | up] matrix so that one product serves both; where a
+    kernel carries the activation in its epilogue the [T, 2 * intermediate] product never exists in memory."""
 
     def __init__(self, rt: Runtime, prefix: str, hidden_size: int, intermediate_size: int):
         super().__init__(rt, prefix)
@@ -30,16 +32,18 @@ class SwiGLU(Part):
         self.w_gate_up = torch.cat([t[self.name("gate_proj.weight")], t[self.name("up_proj.weight")]], 0).contiguous()
         self.w_down = t[self.name("down_proj.weight")].contiguous()
 
-    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        rt, ops = self.rt, self.rt.ops
-        T = h.shape[0]
-        act = rt.buffer("act", T, self.inter, rt.dtype)
-        fused = getattr(ops, "linear_swiglu_supports", None)
-        if fused is not None and fused(h, self.w_gate_up, act):
-            ops.linear_swiglu(h, self.w_gate_up, act)         # product and activation in one kernel
-        else:
-            gate_up = rt.buffer("gate_up", T, 2 * self.inter, rt.dtype)
-            ops.linear(h, self.w_gate_up, gate_up)
-            ops.swiglu(gate_up, act)
-        delta = rt.buffer("ffn_out", T, self.hidden, torch.float32)
-        return ops.linear(act, self.w_down, delta)
+    def emit(self, plan: Plan, h: torch.Tensor) -> torch.Tensor:
+        rt = self.rt
+        act = rt.workspace("act", self.inter, rt.dtype)
+        gate_up = rt.workspace("gate_up", 2 * self.inter, rt.dtype)
+        plan.linear_swiglu(h, self.w_gate_up, gate_up, act)
+        delta = rt.workspace("ffn_out", self.hidden, torch.float32)
+        plan.linear(act, self.w_down, delta)
+        return delta
+
+    def forward(self, h: torch.Tensor, batch=None) -> torch.Tensor:
+        from ..engine.batch import StepBatch
+        plan = Plan()
+        delta = self.emit(plan, h)
+        run_alone(self.rt, plan, batch if batch is not None else StepBatch.bare(h.shape[0], h.device))
+        return delta[: h.shape[0]]

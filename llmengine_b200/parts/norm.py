@@ -5,7 +5,8 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import Part, Runtime, WeightSpec, register_part
+from ..engine.plan import ROWS_LOGITS, ROWS_TOKENS, Plan
+from .base import Part, Runtime, WeightSpec, register_part, run_alone
 
 
 @register_part("norm", "rmsnorm")
@@ -27,8 +28,15 @@ class RMSNorm(Part):
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.gain = tensors[self.name("weight")]
 
+    def emit(self, plan: Plan, x: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: str = ROWS_TOKENS) -> torch.Tensor:
+        out = self.rt.workspace("normed" if rows == ROWS_TOKENS else "normed_rows", self.size, self.rt.dtype)
+        plan.rmsnorm(x, self.gain, self.eps, out, delta=delta, rows=rows)
+        return out
+
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None,
                 out_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        n = x.shape[0] if out_rows is None else out_rows.numel()
-        out = self.rt.buffer("normed" if out_rows is None else "normed_rows", n, self.size, self.rt.dtype)
-        return self.rt.ops.rmsnorm(x, self.gain, self.eps, out, delta=delta, rows=out_rows)
+        from ..engine.batch import StepBatch
+        plan = Plan()
+        out = self.emit(plan, x, delta=delta, rows=ROWS_TOKENS if out_rows is None else ROWS_LOGITS)
+        run_alone(self.rt, plan, StepBatch.bare(x.shape[0], x.device, logit_rows=out_rows))
+        return out[: x.shape[0] if out_rows is None else out_rows.numel()]

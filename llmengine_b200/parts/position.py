@@ -23,6 +23,8 @@ class RotaryEncoding(Part):
     identical values.
     """
 
+    needs_apply = False           # the fused kernels rotate with `rotary_table()`
+
     def __init__(self, rt: Runtime, prefix: str, head_dim: int, theta: float, max_positions: int):
         super().__init__(rt, prefix)
         if head_dim % 2:

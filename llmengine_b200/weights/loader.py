@@ -69,12 +69,10 @@ def load_model_weights(model, config, model_dir: str, compute: torch.dtype, devi
                 raise WeightError(f"tensor {name!r} appears twice in {model_dir} (as {where[name][1]!r} and {raw!r})")
             where[name] = (f, raw)
     specs = model.weight_specs()
-    ignorable = []
-    if getattr(config, "tie_word_embeddings", False) and "lm_head.weight" in where and "lm_head.weight" not in specs:
-        # tied models are sometimes saved with a copy of the table under the head's name
-        print("[llmengine_b200] tie_word_embeddings is set: the file's lm_head.weight is ignored, "
-              "the embedding table is used", file=sys.stderr)
-        ignorable.append("lm_head.weight")
+    # a tensor that a part shares with another part (a tied head) is sometimes stored all the same, as a copy
+    ignorable = [n for n in model.tied_tensors() if n in where and n not in specs]
+    for n in ignorable:
+        print(f"[llmengine_b200] {n} is tied to {model.tied_tensors()[n]}: the file's copy is ignored", file=sys.stderr)
     check_names_and_shapes(specs, {n: f.shape(raw) for n, (f, raw) in where.items()}, ignorable)
     tensors: Dict[str, torch.Tensor] = {}
     for name, spec in specs.items():

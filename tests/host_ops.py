@@ -17,6 +17,12 @@ class HostOps:
     def require(self, *names):
         return None
 
+    def choose_kernels(self, kernels):
+        return None
+
+    def compile(self, plan):
+        return HostPlan(self, plan)
+
     def embedding(self, ids, table, out):
         out.copy_(table[ids.long()].float())
         return out
@@ -113,3 +119,69 @@ class HostOps:
             out[r] = plain_sample(logits[r], greedy=bool(greedy[r]), temperature=float(temperature[r]),
                                   top_k=int(top_k[r]), top_p=float(top_p[r]), u=float(u[r]))
         return out
+
+
+class HostPlan:
+    """A plan interpreted on the CPU: every record runs on the first rows of its buffers, as the native
+    executor runs it on the device."""
+
+    def __init__(self, ops, plan):
+        self.ops, self.plan = ops, plan
+
+    def run(self, batch, first=0, count=-1):
+        o = self.ops
+        T, NL = batch.num_tokens, batch.logit_rows.numel()
+        last = len(self.plan.ops) if count < 0 else first + count
+
+        def n_rows(kind):
+            return NL if kind == "logits" else T
+
+        def cut(t, n=T):
+            return None if t is None else t[:n]
+        for op in self.plan.ops[first:last]:
+            a, k = op.a, op.kind
+            if k == "embedding":
+                o.embedding(batch.token_ids, a["table"], a["out"][:T])
+            elif k == "rmsnorm":
+                some = a["rows"] == "logits"
+                o.rmsnorm(a["x"][:T], a["gain"], a["eps"], a["out"][:n_rows(a["rows"])], delta=cut(a["delta"]),
+                          rows=batch.logit_rows if some else None)
+            elif k == "linear":
+                n = n_rows(a["rows"])
+                if n:
+                    o.linear(a["x"][:n], a["w"], batch.logits if a["out"] is None else a["out"][:n])
+            elif k == "linear_swiglu":
+                o.linear(a["x"][:T], a["w_gate_up"], a["gate_up"][:T])
+                o.swiglu(a["gate_up"][:T], a["out"][:T])
+            elif k == "qkv_post":
+                self._qkv_post(a, batch, T)
+            elif k == "attend":
+                self._attend(a, batch, T)
+            elif k == "attention":
+                nh, nkv, hd = a["num_heads"], a["num_kv_heads"], a["head_dim"]
+                qs, kvs = nh * hd, nkv * hd
+                qkv, w = a["qkv"], a["writes"]
+                self._qkv_post(dict(a, q_in=qkv[:, :qs], k_in=qkv[:, qs:qs + kvs] if w else None,
+                                    v_in=qkv[:, qs + kvs:] if w else None, q_out=a["q"], k_out=None,
+                                    cache=a["cache"] if w else None), batch, T)
+                self._attend(a, batch, T)
+            elif k == "call":
+                a["fn"](batch)
+            else:
+                raise ValueError(k)
+
+    def _qkv_post(self, a, batch, T):
+        cut = lambda t: None if t is None else t[:T]
+        g = batch.groups[a["group"]] if a.get("cache") is not None else None
+        self.ops.qkv_post(q_in=cut(a.get("q_in")), k_in=cut(a.get("k_in")), v_in=cut(a.get("v_in")), num_heads=a["num_heads"],
+                          num_kv_heads=a["num_kv_heads"], head_dim=a["head_dim"], q_gain=a.get("q_gain"), k_gain=a.get("k_gain"),
+                          eps=a.get("eps", 0.0), cos_sin=a.get("cos_sin"), positions=batch.positions, q_out=cut(a.get("q_out")),
+                          k_out=cut(a.get("k_out")), cache=a.get("cache"), slot_mapping=g.slot_mapping if g else None,
+                          page_size=g.page_size if g else 0)
+
+    def _attend(self, a, batch, T):
+        g = batch.groups[a["group"]]
+        self.ops.attention_plain(q=a["q"][:T], cache=a["cache"], out=a["out"][:T], positions=batch.positions,
+                                 token_request=batch.token_request, block_tables=g.block_tables, num_heads=a["num_heads"],
+                                 num_kv_heads=a["num_kv_heads"], head_dim=a["head_dim"], page_size=g.page_size,
+                                 window=a["window"], scale=a["scale"])

@@ -484,3 +484,193 @@ def test_toy_routed_feed_forward_and_position_encoding_on_the_host():
 @pytest.mark.gpu
 def test_toy_routed_feed_forward_and_position_encoding_register_build_and_step():
     _toy_routed_roundtrip(None, DEV)
+
+
+# ----------------------------------------------------------------------------- a cache kind and a block shape of their own
+class SplitKVSpec:
+    """A paged cache whose keys and values have different widths: one row [key | value] per position.  Defined
+    here, outside the package: the cache manager and the engine only use the protocol (paged, window, allocate,
+    bytes_per_token, view)."""
+
+    paged, window = True, 0
+
+    def __init__(self, key_dim, value_dim):
+        self.key_dim, self.value_dim = key_dim, value_dim
+
+    def __eq__(self, other):
+        return isinstance(other, SplitKVSpec) and (self.key_dim, self.value_dim) == (other.key_dim, other.value_dim)
+
+    def allocate(self, count, page_size, dtype, device):
+        return torch.zeros(count, page_size, self.key_dim + self.value_dim, dtype=torch.float32, device=device)
+
+    def bytes_per_token(self, dtype):
+        return 4 * (self.key_dim + self.value_dim)
+
+    def view(self, tensor, group, writes):
+        return {"rows": tensor, "group": group}
+
+
+@register_part("mixer", "toy_split_kv_attention")
+class ToySplitKVAttention(Part):
+    """One-head causal attention with keys of width `key_dim` and values of another width `value_dim`, kept in
+    a cache of its own layout.  Plain tensor operations; it exists only to show that a mixer with another kind
+    of cache plugs in."""
+
+    capture_safe = False
+
+    def __init__(self, rt, prefix, hidden_size, key_dim, value_dim):
+        super().__init__(rt, prefix)
+        self.hidden, self.dk, self.dv = hidden_size, key_dim, value_dim
+
+    def weight_specs(self):
+        return {self.name("q.weight"): WeightSpec((self.dk, self.hidden)), self.name("k.weight"): WeightSpec((self.dk, self.hidden)),
+                self.name("v.weight"): WeightSpec((self.dv, self.hidden)), self.name("o.weight"): WeightSpec((self.hidden, self.dv))}
+
+    def load_weights(self, t):
+        self.wq, self.wk, self.wv, self.wo = (t[self.name(n + ".weight")].float() * 8.0 for n in "qkvo")
+
+    def cache_spec(self):
+        return SplitKVSpec(self.dk, self.dv)
+
+    @staticmethod
+    def attend(q, k, v):
+        T = q.shape[0]
+        s = (q @ k.t()) / math.sqrt(q.shape[1])
+        n = k.shape[0]
+        mask = torch.arange(n, device=q.device)[None, :] > (torch.arange(T, device=q.device)[:, None] + (n - T))
+        return torch.softmax(s.masked_fill(mask, float("-inf")), -1) @ v
+
+    def forward(self, h, batch, cache):
+        g = batch.groups[cache["group"]]
+        rows = cache["rows"].view(-1, self.dk + self.dv)
+        hf = h.float()
+        q, k, v = hf @ self.wq.t(), hf @ self.wk.t(), hf @ self.wv.t()
+        rows[g.slot_mapping.long()] = torch.cat([k, v], dim=1)
+        out = torch.empty(h.shape[0], self.dv, device=h.device)
+        tables, slots = g.block_tables.cpu(), batch.state_slots.tolist()
+        a = 0
+        for r, n in enumerate(batch.q_lens):
+            ctx = batch.start_positions[r] + n
+            pos = torch.arange(ctx)
+            where = (tables[slots[r]][pos // g.page_size].long() * g.page_size + pos % g.page_size).to(h.device)
+            kv = rows[where]
+            out[a:a + n] = self.attend(q[a:a + n], kv[:, :self.dk], kv[:, self.dk:])
+            a += n
+        return out @ self.wo.t()
+
+
+@register_part("block", "toy_postnorm")
+class ToyPostNormBlock(Part):
+    """x = norm(x + mixer(x)): a norm after the residual sum, no feed-forward.  It reads the parts "mixer" and
+    "post_norm" of its layer: another set of roles than the package's block has."""
+
+    capture_safe = False
+
+    def __init__(self, rt, prefix, layer):
+        super().__init__(rt, prefix)
+        self.mixer = build_part("mixer", layer.parts["mixer"], rt, self.name("mixer"))
+        self.post_norm = build_part("norm", layer.parts["post_norm"], rt, self.name("post_norm"))
+
+    def weight_specs(self):
+        return {**self.mixer.weight_specs(), **self.post_norm.weight_specs()}
+
+    def load_weights(self, t):
+        for p in (self.mixer, self.post_norm):
+            p.load_weights({n: t[n] for n in p.weight_specs()})
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, x, delta, batch, cache):
+        if delta is not None:
+            x += delta.float()
+        y = x + self.mixer.forward(x.to(self.rt.dtype), batch, cache)
+        x.copy_(self.post_norm.forward(y).float())        # the package's norm part, run by itself
+        return x, None
+
+
+class ToySplitConfig(ToyConfig):
+    ARCHITECTURE = "ToySplitKVForCausalLM"
+
+    def model_spec(self):
+        H, d = self.hidden_size, self.d
+        norm = PartSpec("rmsnorm", {"size": H, "eps": d["eps"]})
+        split = PartSpec("toy_split_kv_attention", {"hidden_size": H, "key_dim": d["key_dim"], "value_dim": d["value_dim"]})
+        attn = PartSpec("gqa_attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                                          "qk_norm_eps": d["eps"], "window": 0,
+                                          "position_encoding": PartSpec("rope", {"head_dim": 16, "theta": 100.0,
+                                                                                  "max_positions": d["max_positions"]})})
+        ffn = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": d["inter"]})
+        layers = (LayerSpec("layers.0", PartSpec("toy_postnorm"), parts={"mixer": split, "post_norm": norm}),
+                  LayerSpec("layers.1", PartSpec("prenorm_residual"), attn, norm, ffn, norm),
+                  LayerSpec("layers.2", PartSpec("toy_postnorm"), parts={"mixer": split, "post_norm": norm}))
+        return ModelSpec(self.ARCHITECTURE, H, self.vocab_size, d["max_positions"],
+                         PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": H}), layers,
+                         tuple(LayerRun(i) for i in range(3)), norm,
+                         PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": H,
+                                              "tied_to": "embedding.weight"}))
+
+
+if ToySplitConfig.ARCHITECTURE not in ARCHITECTURES:
+    register_architecture(ToySplitConfig.ARCHITECTURE, ToySplitConfig)
+
+TOY_SPLIT = {"architectures": [ToySplitConfig.ARCHITECTURE], "vocab_size": 101, "hidden_size": 32, "inter": 48, "eps": 1e-5,
+             "key_dim": 24, "value_dim": 8, "max_positions": 256}
+
+
+def _plain_toy_split(eng, ids):
+    m = eng.model
+    f = lambda t: t.float().cpu()
+    x = pm.embedding(f(m.embedding.table), ids)
+    T = len(ids)
+    for blk in m.blocks:
+        if isinstance(blk, ToyPostNormBlock):
+            mx = blk.mixer
+            q, k, v = x @ f(mx.wq).t(), x @ f(mx.wk).t(), x @ f(mx.wv).t()
+            x = pm.rms_norm(x + ToySplitKVAttention.attend(q, k, v) @ f(mx.wo).t(), f(blk.post_norm.gain), blk.post_norm.eps)
+        else:
+            mx = blk.mixer
+            h = pm.rms_norm(x, f(blk.mixer_norm.gain), blk.mixer_norm.eps)
+            qkv = pm.linear(h, f(mx.w_qkv))
+            pos = torch.arange(T)
+            q = pm.rope(pm.qk_norm(qkv[:, :mx.q_size].view(T, mx.nh, mx.hd), f(mx.q_gain), mx.eps), pos, 100.0)
+            k = pm.rope(pm.qk_norm(qkv[:, mx.q_size:mx.q_size + mx.kv_size].view(T, mx.nkv, mx.hd), f(mx.k_gain), mx.eps), pos, 100.0)
+            v = qkv[:, mx.q_size + mx.kv_size:].view(T, mx.nkv, mx.hd)
+            x = x + pm.linear(pm.attention(q, k, v).reshape(T, -1), f(mx.w_o))
+            h = pm.rms_norm(x, f(blk.ffn_norm.gain), blk.ffn_norm.eps)
+            gu = pm.linear(h, f(blk.ffn.w_gate_up))
+            x = x + pm.linear(pm.swiglu(gu[:, :blk.ffn.inter], gu[:, blk.ffn.inter:]), f(blk.ffn.w_down))
+    return pm.linear(pm.rms_norm(x, f(m.final_norm.gain), m.final_norm.eps), f(m.head.weight))
+
+
+def _toy_split_roundtrip(ops, device):
+    from helpers import random_ids, replay, trace_mixed, trace_portions, trace_whole, max_live_tokens
+    reqs = {f"r{i}": random_ids(n, 101, 20 + i) for i, n in enumerate([40, 9, 66, 23])}
+    steps_by = {"whole": trace_whole(reqs), "portions": trace_portions(reqs, sizes=(16, 3, 2, 9, 1)),
+                "mixed": trace_mixed(reqs, {r: max(1, len(v) - 6) for r, v in reqs.items()}, max_live=3, seed=2)}
+    want = None
+    for what, steps in steps_by.items():
+        pool = max_live_tokens(steps, 8)
+        ec = EngineConfig(dtype="float32", page_size=8, max_cached_tokens=pool, max_num_seqs=4, max_num_batched_tokens=pool,
+                          device=device, use_cuda_graphs=False)
+        eng = Engine(config=TOY_SPLIT, random_seed=31, engine_config=ec, ops=ops)
+        assert eng.model.head.weight.data_ptr() == eng.model.embedding.table.data_ptr()      # tied through the spec
+        assert [type(s).__name__ for s, _ in eng.model.cache_specs()] == ["SplitKVSpec", "PagedKVSpec", "SplitKVSpec"]
+        assert eng.cache.kv[0].shape[1:] == (8, 32) and eng.cache.kv[1].shape[1:] == (2, 2, 8, 16)
+        if want is None:
+            want = {r: _plain_toy_split(eng, ids) for r, ids in reqs.items()}
+        got = replay(eng, steps)
+        for r in reqs:
+            assert (got[r].cpu() - want[r]).abs().max() < 2e-4, (what, r)
+        eng.cache.check_invariants()
+        assert not eng.cache.requests
+
+
+def test_toy_cache_kind_and_block_shape_on_the_host():
+    from host_ops import HostOps
+    _toy_split_roundtrip(HostOps(), "cpu")
+
+
+@pytest.mark.gpu
+def test_toy_cache_kind_and_block_shape_register_build_and_replay():
+    _toy_split_roundtrip(None, DEV)
