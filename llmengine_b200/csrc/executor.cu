@@ -58,7 +58,7 @@ struct Blas {
             if (lib) break;
         }
         if (!lib)
-            for (const char* name : {"libcublas.so.12", "libcublas.so"}) {
+            for (const char* name : {"libcublas.so.12", "libcublas.so", "/usr/local/cuda/lib64/libcublas.so.12", "/usr/local/cuda/lib64/libcublas.so"}) {
                 lib = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
                 if (lib) break;
             }

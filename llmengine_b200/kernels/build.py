@@ -33,6 +33,8 @@ SOURCES: Dict[str, str] = {
     "utility": "utility.cu",
     # the step executor (host code): walks a model's plan and launches the kernels of the other libraries
     "executor": "executor.cu",
+    # the engine as a C++ library (include/llmengine_b200/engine.h): native host code over the executor and the kernels
+    "engine": "native/engine.cu",
     # compiled per head size: ask for "attention_fast@HEAD_DIM=128"
     "attention_fast": "attention_fast.cu",
     # the tcgen05 portion kernel, per head size (64 or 128): "attention_tc@HEAD_DIM=128"
@@ -54,7 +56,7 @@ VARIANTS: Dict[str, List[str]] = {
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 
 # link flags of single libraries
-LINK: Dict[str, List[str]] = {"executor": ["-ldl"]}
+LINK: Dict[str, List[str]] = {"executor": ["-ldl"], "engine": ["-ldl"]}
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -110,15 +112,22 @@ def _digest(key: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS + defines).encode())
     for fn in sorted(os.listdir(CSRC)):
-        if fn.endswith((".cuh", ".h")) or fn == SOURCES[name] or fn in INCLUDES.get(name, ()):
+        if (fn.endswith((".cuh", ".h")) or fn == SOURCES[name] or fn in INCLUDES.get(name, ())) and os.path.isfile(os.path.join(CSRC, fn)):
             with open(os.path.join(CSRC, fn), "rb") as f:
                 h.update(fn.encode())
                 h.update(f.read())
-    for root, _dirs, files in sorted(os.walk(INCLUDE)):
-        for fn in sorted(files):
-            with open(os.path.join(root, fn), "rb") as f:
+    if os.path.dirname(SOURCES[name]):                      # a source in a folder of its own: its neighbours count
+        sub = os.path.join(CSRC, os.path.dirname(SOURCES[name]))
+        for fn in sorted(os.listdir(sub)):
+            with open(os.path.join(sub, fn), "rb") as f:
                 h.update(fn.encode())
                 h.update(f.read())
+    if name in ("executor", "engine"):                      # the libraries behind the public headers
+        for root, _dirs, files in sorted(os.walk(INCLUDE)):
+            for fn in sorted(files):
+                with open(os.path.join(root, fn), "rb") as f:
+                    h.update(fn.encode())
+                    h.update(f.read())
     return h.hexdigest()[:12]
 
 
@@ -167,11 +176,58 @@ def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) 
             if time.time() - last > 8:
                 last = time.time()
                 _log(f"still compiling {', '.join(sorted(pending))} ({last - t0:.0f} s)")
+    write_manifest(names)
     return paths
 
 
-def build_all() -> Dict[str, str]:
+def all_keys() -> List[str]:
     keys = [n for n in SOURCES if n not in VARIANTS]
     for v in VARIANTS.values():
         keys.extend(v)
-    return ensure_built(keys)
+    return keys
+
+
+def write_manifest(more: Iterable[str] = ()) -> str:
+    """`manifest.json` in the build folder: library key -> file name, for every library that is built.  The C++
+    front (include/llmengine_b200/engine.h) finds the kernel libraries through it."""
+    import json
+    d = build_dir()
+    path = os.path.join(d, "manifest.json")
+    try:
+        with open(path, "r", encoding="utf-8") as f:
+            known = json.load(f)
+    except (OSError, ValueError):
+        known = {}
+    for key in list(all_keys()) + list(more):
+        p = library_path(key)
+        if os.path.exists(p):
+            known[key] = os.path.basename(p)
+    known = {k: v for k, v in known.items() if os.path.exists(os.path.join(d, v))}
+    tmp = f"{path}.{os.getpid()}.tmp"
+    with open(tmp, "w", encoding="utf-8") as f:
+        json.dump(known, f, indent=1, sort_keys=True)
+    os.replace(tmp, path)
+    if "engine" in known:                 # a fixed name to link a C++ program against (-lllmengine_b200)
+        link = os.path.join(d, "libllmengine_b200.so")
+        try:
+            if os.path.islink(link) or os.path.exists(link):
+                os.unlink(link)
+            os.symlink(known["engine"], link)
+        except OSError:
+            pass
+    return path
+
+
+def build_all() -> Dict[str, str]:
+    paths = ensure_built(all_keys())
+    write_manifest()
+    return paths
+
+
+if __name__ == "__main__":
+    # python -m llmengine_b200.kernels.build [library keys ...]: compile them (all of them without arguments)
+    import sys as _sys
+    built = ensure_built(_sys.argv[1:]) if len(_sys.argv) > 1 else build_all()
+    write_manifest(built)
+    for k, v in built.items():
+        print(f"{k}: {v}")

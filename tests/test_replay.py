@@ -292,3 +292,40 @@ def test_logits_of_captured_decode_steps(tmp_path, monkeypatch, name, dtype, sho
     assert any(k[0] == 2 for k in eng._graphs)
     eng.cache.check_invariants()
     eng.check_kernels()
+
+
+# ----------------------------------------------------------------------------- one kernel exchanged for another inside the model
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernels", ["plain", {"attention.portion": "mma"}, {"attention.decode": "split"},
+                                     {"attention": "plain"}, {"linear": "cublas"}, {"linear": "tcgen05"},
+                                     {"linear.decode": "cublas"}, {"linear_swiglu": "unfused"}])
+def test_single_kernels_exchanged_inside_the_model(tmp_path, kernels):
+    """`EngineConfig.kernels` as a mapping operation -> variant: the whole model runs with one kernel exchanged for its
+    twin (the mma.sync portion attention for the tcgen05 one, the unfused decode attention, the library product, ...)
+    and still gives the plain implementation's logits.  This is the tool that narrows a wrong logit down to a kernel."""
+    d, page, reqs, ref, tol = _setup(tmp_path, "D", "bfloat16", 2.0)
+    steps = _traces(reqs)["mixed"]
+    eng = engine_for(d, "bfloat16", max_live_tokens(steps, 64), page_size=page, kernels=kernels)
+    if isinstance(kernels, dict):
+        for op, variant in kernels.items():
+            assert eng.ops.chosen(op) == variant
+    else:
+        assert eng.ops.chosen("attention") == "plain" and eng.ops.chosen("linear") == "plain"
+    before = eng.ops.launches
+    got = replay(eng, steps, poison=True)
+    compare(got, ref, tol, f"kernels={kernels}")
+    assert eng.ops.launches > before
+    eng.check_kernels()
+
+
+@pytest.mark.gpu
+def test_an_unknown_operation_or_variant_is_refused():
+    from llmengine_b200.kernels.ops import CudaOps, KernelError
+    ops = CudaOps(torch.device("cuda:0"))
+    with pytest.raises(KernelError, match="no operation 'softmax'"):
+        ops.choose("softmax", "fast")
+    with pytest.raises(KernelError, match="has no variant 'wgmma'"):
+        ops.choose("linear", "wgmma")
+    with pytest.raises(Exception, match="kernels must be"):
+        from llmengine_b200.config import EngineConfig
+        EngineConfig(kernels="fastest")
