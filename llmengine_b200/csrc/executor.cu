@@ -142,6 +142,8 @@ const char* kind_name(int kind) {
     return kind >= 1 && kind <= 8 ? names[kind] : names[0];
 }
 
+constexpr int SKINNY_ROWS = 32;      // most rows the weight-streaming product takes (gemm_skinny.cu)
+
 bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr) {
     return (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
 }
@@ -197,7 +199,7 @@ int product(LlmeExecutor& ex, const LlmeStep& step, const void* x, long long ldx
     if (w_dtype != LLME_DT_BF16) return ex.fail("linear: bfloat16 inputs need bfloat16 weights");
     const std::string& how = ex.choice("linear");
     const bool operands_ok = K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && aligned16(x, w);
-    if (how != "plain" && M <= 16 && operands_ok && ex.choice("linear.decode") == "skinny") {
+    if (how != "plain" && M <= SKINNY_ROWS && operands_ok && ex.choice("linear.decode") == "skinny") {
         if (auto* f = (GemmBf16Fn)ex.find("gemm_skinny"))     // a handful of tokens: the weight-streaming kernel
             return ex.launched(f(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, stream), "gemm_skinny");
     }
@@ -235,7 +237,7 @@ int op_linear_swiglu(LlmeExecutor& ex, const LlmeLinearSwigluOp& o, const LlmeSt
     if (M <= 0) return 0;
     const bool fused = ex.choice("linear_swiglu") == "fused" && ex.choice("linear") != "plain" && o.dtype == LLME_DT_BF16;
     const bool operands_ok = o.k % 8 == 0 && o.ldx % 8 == 0 && o.ldw % 8 == 0 && aligned16(o.x, o.w_gate_up);
-    if (fused && M <= 16 && operands_ok && ex.choice("linear.decode") == "skinny") {
+    if (fused && M <= SKINNY_ROWS && operands_ok && ex.choice("linear.decode") == "skinny") {
         if (auto* f = (GemmBf16Fn)ex.find("gemm_skinny_swiglu"))
             return ex.launched(f(o.x, o.ldx, o.w_gate_up, o.ldw, o.out, LLME_DT_BF16, o.ldo, M, o.inter, o.k, st), "gemm_skinny_swiglu");
     }

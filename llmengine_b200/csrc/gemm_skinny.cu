@@ -1,4 +1,4 @@
-// out[M,N] = x[M,K] * W[N,K]^T for a handful of tokens (M <= 16), bfloat16 operands, 32-bit
+// out[M,N] = x[M,K] * W[N,K]^T for a handful of tokens (M <= 32), bfloat16 operands, 32-bit
 // accumulation: the matrix product of a decode step, which is bound by reading W once from HBM.
 //
 // The roles are swapped with respect to a large product: 16 rows of W are the M side of a
@@ -33,7 +33,9 @@ typedef __nv_bfloat16 bf16;
 constexpr int KC = 64;            // k values per chunk (two blocks of 32)
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-constexpr int UNROLL = 4;         // chunks whose loads are issued together
+// chunks whose loads are issued together: four for up to 16 tokens; two beyond, where the tokens' own operands
+// take the registers
+__host__ __device__ constexpr int unroll_for(int mt) { return mt <= 2 ? 4 : 2; }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -55,9 +57,10 @@ struct SkinnyArgs {
     int inter;      // 0: plain product; > 0: W = [gate | up] of `inter` rows each and out = silu(gate) * up
 };
 
-// MT: 8-token tiles (1: M <= 8, 2: M <= 16).
+// MT: 8-token tiles (1: M <= 8, 2: M <= 16, 3: M <= 24, 4: M <= 32).
 template <int MT, typename O>
 __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
+    constexpr int UNROLL = unroll_for(MT);
     __shared__ float red[WARPS][MT * 8][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int quad = lane & 3, r = lane >> 2;
@@ -186,14 +189,17 @@ int launch(const SkinnyArgs& a, cudaStream_t s) {
 
 template <typename O>
 int dispatch(const SkinnyArgs& a, cudaStream_t s) {
-    return a.M <= 8 ? launch<1, O>(a, s) : launch<2, O>(a, s);
+    if (a.M <= 8) return launch<1, O>(a, s);
+    if (a.M <= 16) return launch<2, O>(a, s);
+    if (a.M <= 24) return launch<3, O>(a, s);
+    return launch<4, O>(a, s);
 }
 
 }  // namespace
 
 // 1 if llme_gemm_skinny_bf16 takes this problem, 0 if the caller should use the general product.
 LLME_API int llme_gemm_skinny_supports(int M, int N, int K, long long ldx, long long ldw) {
-    return M >= 1 && M <= 16 && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
+    return M >= 1 && M <= 32 && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
 }
 
 // x [M,K] and W [N,K] bfloat16 with row strides ldx, ldw (elements); out [M,N] float (out_dtype 0) or
@@ -202,7 +208,7 @@ LLME_API int llme_gemm_skinny_bf16(const void* x, long long ldx, const void* w, 
                                    long long ldo, int M, int N, int K, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!x || !w || !out) LLME_REFUSE("gemm_skinny: null pointer");
-    if (!llme_gemm_skinny_supports(M, N, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, N, K, ldx, ldw);
+    if (!llme_gemm_skinny_supports(M, N, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 32, K and strides multiples of 8)", M, N, K, ldx, ldw);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (ldo < N) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
     SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, N, K, 0};
@@ -216,7 +222,7 @@ LLME_API int llme_gemm_skinny_swiglu_bf16(const void* x, long long ldx, const vo
                                           int out_dtype, long long ldo, int M, int inter, int K, cudaStream_t stream) {
     if (M <= 0 || inter <= 0) return 0;
     if (!x || !w || !out) LLME_REFUSE("gemm_skinny: null pointer");
-    if (inter > (1 << 29) || !llme_gemm_skinny_supports(M, 2 * inter, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d inter=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, inter, K, ldx, ldw);
+    if (inter > (1 << 29) || !llme_gemm_skinny_supports(M, 2 * inter, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d inter=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 32, K and strides multiples of 8)", M, inter, K, ldx, ldw);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (ldo < inter) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
     SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, 2 * inter, K, inter};

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <memory>
 #include <stdexcept>

@@ -179,9 +179,10 @@ def test_tcgen05_gemm_into_a_strided_unaligned_output(ops):
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 100, 72), (16, 1000, 264), (9, 33, 8),
-                                   (5, 24576, 512), (2, 151936, 128), (8, 4096, 12288)])
+                                   (5, 24576, 512), (2, 151936, 128), (8, 4096, 12288), (17, 4096, 4096), (24, 1000, 264),
+                                   (29, 33, 72), (32, 6144, 4096), (32, 4096, 12288)])
 def test_skinny_gemm(ops, M, N, K, out_dtype):
-    """The decode-step product (at most 16 tokens): rows and widths that are no multiple of the tiles."""
+    """The decode-step product (at most 32 tokens): rows and widths that are no multiple of the tiles."""
     a = _rand(M, K, dtype=torch.bfloat16, seed=40)
     w = _rand(N, K, dtype=torch.bfloat16, seed=41, scale=0.05)
     out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
@@ -197,17 +198,18 @@ def test_skinny_gemm(ops, M, N, K, out_dtype):
 
 
 def test_skinny_gemm_rows_do_not_depend_on_the_batch(ops):
-    a = _rand(16, 1024, dtype=torch.bfloat16, seed=42)
+    a = _rand(32, 1024, dtype=torch.bfloat16, seed=42)
     w = _rand(300, 1024, dtype=torch.bfloat16, seed=43)
-    full = torch.empty(16, 300, device=DEV)
+    full = torch.empty(32, 300, device=DEV)
     ops.linear(a, w, full)
-    for m in (1, 7, 8, 9):
+    for m in (1, 7, 8, 9, 16, 17, 24, 25):
         part = torch.empty(m, 300, device=DEV)
         ops.linear(a[:m].contiguous(), w, part)
         assert torch.equal(part, full[:m])
 
 
-@pytest.mark.parametrize("M,inter,K", [(8, 12288, 4096), (1, 3072, 1024), (16, 100, 72), (3, 8, 8), (11, 5000, 264), (7, 20, 520)])
+@pytest.mark.parametrize("M,inter,K", [(8, 12288, 4096), (1, 3072, 1024), (16, 100, 72), (3, 8, 8), (11, 5000, 264), (7, 20, 520),
+                                       (20, 5000, 264), (32, 12288, 4096), (27, 100, 72)])
 def test_skinny_gemm_with_swiglu(ops, M, inter, K):
     """Product and activation in one kernel against the product followed by the activation kernel (the same
     arithmetic, so the same bits) and against 64-bit arithmetic."""

@@ -95,3 +95,34 @@ def test_the_cpp_front_names_what_is_wrong(tmp_path):
     no_key = tmp_path / "nokey.json"
     no_key.write_text(json.dumps({k: v for k, v in TINY_A.items() if k != "rms_norm_eps"}))
     assert "lacks required key(s): rms_norm_eps" in _native(["--random-config", str(no_key), "1"], expect=1).stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_the_cpp_step_function_replays_a_mixed_trace(tmp_path, name, dtype):
+    """examples/trace_run.cpp: the replay protocol on Engine::step_batch.  Up to four live requests, portions of some
+    beside single tokens of others, so few pages that they are used again; logits against the plain implementation."""
+    import numpy as np
+
+    from helpers import compare, max_live_tokens
+    from test_replay import CONFIGS, _setup, _traces
+    d, page, reqs, ref, tol = _setup(tmp_path, name, dtype, 2.0)
+    steps = _traces(reqs)["mixed"]
+    out = tmp_path / "out"
+    lines = [json.dumps({"step": i, "entries": [{"id": r, "tokens": t, "want": w} for r, t, w in e], "end": end})
+             for i, (e, end) in enumerate(steps)]
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate_native"), "--program", "trace_run", "--model", d,
+                        "--dtype", dtype, "--out", str(out), "--max-tokens", str(max_live_tokens(steps, 64)), "--page-size", str(page)],
+                       input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+    V = CONFIGS[name][0]["vocab_size"]
+    rows = {}
+    for i, (e, _) in enumerate(steps):
+        arr = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V))
+        k = 0
+        for r, t, w in e:
+            rows.setdefault(r, []).append(arr[k:k + len(w)])
+            k += len(w)
+        assert k == arr.shape[0]
+    compare({r: torch.cat(v) for r, v in rows.items()}, ref, tol, f"C++ trace_run/{name}/{dtype}")
