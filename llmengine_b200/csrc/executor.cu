@@ -142,7 +142,19 @@ const char* kind_name(int kind) {
     return kind >= 1 && kind <= 8 ? names[kind] : names[0];
 }
 
-constexpr int SKINNY_ROWS = 32;      // most rows the weight-streaming product takes (gemm_skinny.cu)
+constexpr int SKINNY_ROWS = 16;      // most rows the weight-streaming product takes (gemm_skinny.cu)
+
+// Whether a product of M tokens goes to the weight-streaming kernel when the choice is "auto".  That kernel has one
+// block per group of 16 weight rows (8 gate + 8 up rows with the activation), two blocks resident per SM: it wins
+// against the library's product for up to 8 tokens when its blocks fill their waves (4096 rows: 256 blocks for 296
+// places, 5.5 TB/s on 4096 x 12288 against 3.1), and loses when a second wave is nearly empty (5120 rows: 320 blocks,
+// 4.5 TB/s on 5120 x 17408 against 5.6) or when 9 to 16 tokens double the operands it re-reads from L2 per block.
+bool skinny_pays(const LlmeExecutor& ex, int M, long long row_groups) {
+    if (M > 8) return false;
+    const long long places = 2LL * ex.sms, waves = (row_groups + places - 1) / places;
+    if (4 * row_groups <= places) return true;          // a small product is bound by its launch, not by its waves
+    return 10 * row_groups >= 8 * waves * places;
+}
 
 bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr) {
     return (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
@@ -199,7 +211,8 @@ int product(LlmeExecutor& ex, const LlmeStep& step, const void* x, long long ldx
     if (w_dtype != LLME_DT_BF16) return ex.fail("linear: bfloat16 inputs need bfloat16 weights");
     const std::string& how = ex.choice("linear");
     const bool operands_ok = K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && aligned16(x, w);
-    if (how != "plain" && M <= SKINNY_ROWS && operands_ok && ex.choice("linear.decode") == "skinny") {
+    const std::string& dec = ex.choice("linear.decode");
+    if (how != "plain" && M <= SKINNY_ROWS && operands_ok && (dec == "skinny" || (dec == "auto" && skinny_pays(ex, M, (N + 15) / 16)))) {
         if (auto* f = (GemmBf16Fn)ex.find("gemm_skinny"))     // a handful of tokens: the weight-streaming kernel
             return ex.launched(f(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, stream), "gemm_skinny");
     }
@@ -237,7 +250,8 @@ int op_linear_swiglu(LlmeExecutor& ex, const LlmeLinearSwigluOp& o, const LlmeSt
     if (M <= 0) return 0;
     const bool fused = ex.choice("linear_swiglu") == "fused" && ex.choice("linear") != "plain" && o.dtype == LLME_DT_BF16;
     const bool operands_ok = o.k % 8 == 0 && o.ldx % 8 == 0 && o.ldw % 8 == 0 && aligned16(o.x, o.w_gate_up);
-    if (fused && M <= SKINNY_ROWS && operands_ok && ex.choice("linear.decode") == "skinny") {
+    const std::string& dec = ex.choice("linear.decode");
+    if (fused && M <= SKINNY_ROWS && operands_ok && (dec == "skinny" || (dec == "auto" && skinny_pays(ex, M, (o.inter + 7) / 8)))) {
         if (auto* f = (GemmBf16Fn)ex.find("gemm_skinny_swiglu"))
             return ex.launched(f(o.x, o.ldx, o.w_gate_up, o.ldw, o.out, LLME_DT_BF16, o.ldo, M, o.inter, o.k, st), "gemm_skinny_swiglu");
     }
@@ -376,7 +390,7 @@ int op_attention(LlmeExecutor& ex, const LlmeAttentionOp& o, const LlmeStep& s, 
 const std::map<std::string, std::vector<std::string>>& variants() {
     static const std::map<std::string, std::vector<std::string>> v = {
         {"linear", {"auto", "tcgen05", "cublas", "plain"}},
-        {"linear.decode", {"skinny", "cublas"}},
+        {"linear.decode", {"auto", "skinny", "cublas"}},
         {"linear_swiglu", {"fused", "unfused"}},
         {"attention", {"fast", "plain"}},
         {"attention.portion", {"tcgen05", "mma"}},

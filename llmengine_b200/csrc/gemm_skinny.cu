@@ -1,4 +1,4 @@
-// out[M,N] = x[M,K] * W[N,K]^T for a handful of tokens (M <= 32), bfloat16 operands, 32-bit
+// out[M,N] = x[M,K] * W[N,K]^T for a handful of tokens (M <= 16), bfloat16 operands, 32-bit
 // accumulation: the matrix product of a decode step, which is bound by reading W once from HBM.
 //
 // The roles are swapped with respect to a large product: 16 rows of W are the M side of a
@@ -33,9 +33,7 @@ typedef __nv_bfloat16 bf16;
 constexpr int KC = 64;            // k values per chunk (two blocks of 32)
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-// chunks whose loads are issued together: four for up to 16 tokens; two beyond, where the tokens' own operands
-// take the registers
-__host__ __device__ constexpr int unroll_for(int mt) { return mt <= 2 ? 4 : 2; }
+constexpr int UNROLL = 4;         // chunks whose loads are issued together
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -57,10 +55,11 @@ struct SkinnyArgs {
     int inter;      // 0: plain product; > 0: W = [gate | up] of `inter` rows each and out = silu(gate) * up
 };
 
-// MT: 8-token tiles (1: M <= 8, 2: M <= 16, 3: M <= 24, 4: M <= 32).
+// MT: 8-token tiles (1: M <= 8, 2: M <= 16).  Every block of a token's row re-reads the tokens' operands from L2, so
+// beyond 16 tokens that traffic outgrows the weights' and the library product is faster (measured at 17 to 32 tokens:
+// 2.1 to 3.6 TB/s against 4.1 to 5.2 TB/s).
 template <int MT, typename O>
-__global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
-    constexpr int UNROLL = unroll_for(MT);
+__global__ void __launch_bounds__(THREADS, 2) gemm_skinny_kernel(SkinnyArgs a) {
     __shared__ float red[WARPS][MT * 8][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int quad = lane & 3, r = lane >> 2;
@@ -89,12 +88,16 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f;
 
-    const int chunks = a.K / KC;                      // whole chunks; the rest of K is handled below
+    // A warp takes the chunks warp, warp + 8, ... of K, four at a time with all their loads issued together; a chunk
+    // past the end of K (the last round of a K that is no multiple of 4 x 8 x 64, or the open end of the last chunk)
+    // contributes zeros.  Whatever K is, the loads of a round are in flight together: a round of single chunks at the
+    // end left a K of 5,120 or 17,408 at two thirds of the rate of a K of 4,096.
+    const int chunks_all = (a.K + KC - 1) / KC;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    int c = warp;
     bool first = true;
-    for (; c + (UNROLL - 1) * WARPS < chunks; c += UNROLL * WARPS) {
+    for (int c = warp; c < chunks_all; c += UNROLL * WARPS) {
         uint4 wa[UNROLL][2], wb[UNROLL][2], xv[UNROLL][MT][2];
+        bool ok[UNROLL][2];
         // the weights do not depend on the kernel before this one: the first group of them is requested
         // before waiting for it; x, which that kernel produced, only after
 #pragma unroll
@@ -102,8 +105,9 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
             const int k = (c + q * WARPS) * KC;
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
-                wa[q][b] = load_stream(w0 + k + b * 32);
-                wb[q][b] = load_stream(w1 + k + b * 32);
+                ok[q][b] = k + b * 32 + quad * 8 < a.K;       // K is a multiple of 8: a piece is inside or outside
+                wa[q][b] = ok[q][b] ? load_stream(w0 + k + b * 32) : zero;
+                wb[q][b] = ok[q][b] ? load_stream(w1 + k + b * 32) : zero;
             }
         }
         if (first) {
@@ -117,7 +121,7 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
             for (int b = 0; b < 2; ++b)
 #pragma unroll
                 for (int m = 0; m < MT; ++m)
-                    xv[q][m][b] = xok[m] ? *reinterpret_cast<const uint4*>(xr[m] + k + b * 32) : zero;
+                    xv[q][m][b] = (ok[q][b] && xok[m]) ? *reinterpret_cast<const uint4*>(xr[m] + k + b * 32) : zero;
         }
 #pragma unroll
         for (int q = 0; q < UNROLL; ++q)
@@ -130,23 +134,6 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(SkinnyArgs a) {
                 }
     }
     if (first) pdl_wait();
-    // this warp's remaining chunks, the last of which may be a partial one
-    const int chunks_all = (a.K + KC - 1) / KC;
-    for (; c < chunks_all; c += WARPS) {
-        const int k = c * KC;
-#pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            const bool ok = k + b * 32 + quad * 8 < a.K;      // K is a multiple of 8: a piece is inside or outside
-            const uint4 va = ok ? load_stream(w0 + k + b * 32) : zero;
-            const uint4 vb = ok ? load_stream(w1 + k + b * 32) : zero;
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                const uint4 vx = (ok && xok[m]) ? *reinterpret_cast<const uint4*>(xr[m] + k + b * 32) : zero;
-                mma_bf16(acc[m], va.x, vb.x, va.y, vb.y, vx.x, vx.y);
-                mma_bf16(acc[m], va.z, vb.z, va.w, vb.w, vx.z, vx.w);
-            }
-        }
-    }
 
     pdl_launch_dependents();   // only the short epilogue is left: the next kernel may move in
     // the warps' partial sums, added in a fixed order: value (token, row) at index token * 16 + row
@@ -189,17 +176,14 @@ int launch(const SkinnyArgs& a, cudaStream_t s) {
 
 template <typename O>
 int dispatch(const SkinnyArgs& a, cudaStream_t s) {
-    if (a.M <= 8) return launch<1, O>(a, s);
-    if (a.M <= 16) return launch<2, O>(a, s);
-    if (a.M <= 24) return launch<3, O>(a, s);
-    return launch<4, O>(a, s);
+    return a.M <= 8 ? launch<1, O>(a, s) : launch<2, O>(a, s);
 }
 
 }  // namespace
 
 // 1 if llme_gemm_skinny_bf16 takes this problem, 0 if the caller should use the general product.
 LLME_API int llme_gemm_skinny_supports(int M, int N, int K, long long ldx, long long ldw) {
-    return M >= 1 && M <= 32 && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
+    return M >= 1 && M <= 16 && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
 }
 
 // x [M,K] and W [N,K] bfloat16 with row strides ldx, ldw (elements); out [M,N] float (out_dtype 0) or
@@ -208,7 +192,7 @@ LLME_API int llme_gemm_skinny_bf16(const void* x, long long ldx, const void* w, 
                                    long long ldo, int M, int N, int K, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!x || !w || !out) LLME_REFUSE("gemm_skinny: null pointer");
-    if (!llme_gemm_skinny_supports(M, N, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 32, K and strides multiples of 8)", M, N, K, ldx, ldw);
+    if (!llme_gemm_skinny_supports(M, N, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, N, K, ldx, ldw);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (ldo < N) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
     SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, N, K, 0};
@@ -222,7 +206,7 @@ LLME_API int llme_gemm_skinny_swiglu_bf16(const void* x, long long ldx, const vo
                                           int out_dtype, long long ldo, int M, int inter, int K, cudaStream_t stream) {
     if (M <= 0 || inter <= 0) return 0;
     if (!x || !w || !out) LLME_REFUSE("gemm_skinny: null pointer");
-    if (inter > (1 << 29) || !llme_gemm_skinny_supports(M, 2 * inter, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d inter=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 32, K and strides multiples of 8)", M, inter, K, ldx, ldw);
+    if (inter > (1 << 29) || !llme_gemm_skinny_supports(M, 2 * inter, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d inter=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, inter, K, ldx, ldw);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (ldo < inter) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
     SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, 2 * inter, K, inter};

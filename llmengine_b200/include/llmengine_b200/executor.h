@@ -142,7 +142,7 @@ void llme_executor_destroy(LlmeExecutor*);
 int llme_executor_register(LlmeExecutor*, const char* name, void* entry_point);
 /* Which implementation an operation takes.  Operations and their variants:
  *   "linear":            "auto" | "tcgen05" | "cublas" | "plain"   (bfloat16 products of 128 tokens or more / all)
- *   "linear.decode":     "skinny" | "cublas"                        (bfloat16 products of up to 32 tokens)
+ *   "linear.decode":     "auto" | "skinny" | "cublas"               (bfloat16 products of up to 16 tokens)
  *   "linear_swiglu":     "fused" | "unfused"
  *   "attention.portion": "tcgen05" | "mma" | "plain"
  *   "attention.decode":  "fused" | "split" | "plain"

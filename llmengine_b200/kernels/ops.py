@@ -213,7 +213,8 @@ class CudaOps:
                 if a["x"].dtype == torch.float32:
                     want("gemm_f32")
                 elif self.chosen("linear") != "plain":
-                    want("gemm_skinny")
+                    if self.chosen("linear.decode") != "cublas":
+                        want("gemm_skinny")
                     if self.chosen("linear") != "cublas":
                         want("gemm_tcgen05")
                 if op.kind == "linear_swiglu":
@@ -459,7 +460,7 @@ class CudaOps:
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out[M,N] = x[M,K] @ w[N,K]^T by the kernel the executor chooses for this shape.  32-bit operands: this
         package's FMA kernel (never a reduced-precision mode).  bfloat16 operands: the weight-streaming kernel for
-        up to 32 rows, the tcgen05 kernel for 128 rows or more when its tiles fill the GPU, else cuBLAS with 32-bit
+        up to 16 rows, the tcgen05 kernel for 128 rows or more when its tiles fill the GPU, else cuBLAS with 32-bit
         accumulation; the output in `out`'s type."""
         assert w.shape[1] == x.shape[1] and out.shape == (x.shape[0], w.shape[0])
         self._run_one(lambda plan: plan.linear(x, w, out))
@@ -469,7 +470,7 @@ class CudaOps:
         """Whether a kernel with the activation in its epilogue exists for this product (a handful of rows: the
         weight-streaming kernel; 128 rows or more: the tcgen05 kernel; bfloat16, 16-byte aligned rows)."""
         M, K = x.shape
-        return (x.dtype == w_gate_up.dtype == out.dtype == torch.bfloat16 and (0 < M <= 32 or M >= 128) and K % 8 == 0
+        return (x.dtype == w_gate_up.dtype == out.dtype == torch.bfloat16 and (0 < M <= 16 or M >= 128) and K % 8 == 0
                 and x.stride(1) == 1 and w_gate_up.stride(1) == 1 and out.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w_gate_up.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and out.shape[1] >= 8
                 and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
