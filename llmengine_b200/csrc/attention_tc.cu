@@ -33,12 +33,24 @@
 // llme_attention_tc_status()), and the block drains its copies, frees its tensor memory and returns.  A warp
 // that has given up still attends every named barrier of its pair.
 //
-// Measured (2,048-token prompt, 32 query and 8 key/value heads of 128, B200): 56.5 us (the SM clock is about
-// 1.62 GHz while it runs; a round of sixteen instructions then needs 0.71 us of the pipe, the thread's
-// bookkeeping 0.2 to 0.3 us more, and a tile's softmax about 1 us, of which 0.6 us are its 8,192 exponentials
-// on the two warps a scheduler has of it).  With O_t(i) and S_t(i+1) as separate rounds of eight, each with
-// waits and commits of its own: 62.7 us.  One Q tile per block with P in shared memory took 71 us.  A second
-// issuing warp (one per Q tile) made it slower (66.8 us).
+// Measured (2,048-token prompt, 32 query and 8 key/value heads of 128, B200): 53 us with pages of 64 tokens, 57 us
+// with pages of 16 (the SM clock is about 1.62 GHz while it runs; a round of sixteen instructions then needs 0.71 us
+// of the pipe, the thread's bookkeeping 0.2 to 0.3 us more, and a tile's softmax about 1 us, of which 0.6 us are its
+// 8,192 exponentials on the two warps a scheduler has of it).  Storing the output straight from the threads that
+// hold it (16 bytes a lane, every lane another row) cost 1.4 us a block, 3 to 4 us of the launch; through shared
+// memory it is whole rows.  With O_t(i) and S_t(i+1) as separate rounds of eight, each with waits and commits of its
+// own: 62.7 us.  One Q tile per block with P in shared memory took 71 us.  A second issuing warp (one per Q tile)
+// made it slower (66.8 us).
+//
+// Also tried and dropped, each correct and each slower (62 to 65 us): one block per SM that walks a list of
+// 128-row items (queries and probabilities in tensor memory, four threads a row, the scores one or two key tiles
+// ahead of the outputs, separate loader warps for keys and values, the items of a block decoded at once during
+// set-up).  It removes the 5 us a block spends before its first and after its last tile, but a key tile of
+// 128 x 128 took it 1.40 to 1.45 us whatever ran ahead: the thread that issues the matrix instructions and the
+// softmax warps were each busy for that long.  Sixteen instructions keep the issuing thread for 0.8 to 0.9 us (the
+// pipe takes few in advance, so their issue runs at the pipe's pace), its waits and commits for 0.5 us more, during
+// which the pipe drains; a tile's softmax took 0.85 us of exponentials plus 0.4 us to hand the probabilities over.
+// Two Q tiles that share every key tile, as here, pay those once for 256 rows.
 //
 // Reference counterpart: flash_sdpa_tiled_kernel (src/runtime/kernels/cuda_kernels.cu:558-645): one block per
 // query row, scalar FMA, keys of the same launch only.
@@ -607,26 +619,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             bar->row_sum[t][ch][row] = l_run;
             pair_sync();
             l_run += bar->row_sum[t][ch ^ 1][row];
-            if (ok && !*abort_flag) {
+            // The output goes through shared memory, through the Q tile's place, which nothing reads any more: a
+            // thread holds half of ONE row, and rows lie 2 x HEAD_DIM bytes apart in the output, so that a warp's
+            // store of 16 bytes a lane would touch 32 lines (1.4 us for the block's 16 warps).  The 16-byte pieces
+            // of a row are swizzled with the row, so that neither the writes (eight rows, the same piece) nor the
+            // reads (one row, pieces in turn) meet in a bank; the two warps of a (Q tile, quarter) then write their
+            // 32 rows out whole, two rows to a store.
+            constexpr int ROW_PIECES = HD / 8;
+            unsigned char* stage = q_tiles + t * TILE_BYTES;     // [BM rows][2 x HEAD_DIM bytes]
+            const bool good = ok && !*abort_flag;
+            if (good) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float inv = 1.0f / l_run;
-                bf16* dst = a.out + ((size_t)(q0 + m / G) * a.nh + kvh * G + m % G) * HD + ch * OC;
 #pragma unroll 1
                 for (int c = 0; c < OC; c += 32) {
                     float v[32];
                     tmem_ld32(tmem_o[t] + lane_off + (unsigned)(ch * OC + c), v);
-                    if (row_ok) {
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            uint4 pk;
-                            unsigned* pw = reinterpret_cast<unsigned*>(&pk);
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 pk;
+                        unsigned* pw = reinterpret_cast<unsigned*>(&pk);
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                __nv_bfloat162 hh = __floats2bfloat162_rn(v[q4 * 8 + 2 * e] * inv, v[q4 * 8 + 2 * e + 1] * inv);
-                                pw[e] = *reinterpret_cast<unsigned*>(&hh);
-                            }
-                            *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(v[q4 * 8 + 2 * e] * inv, v[q4 * 8 + 2 * e + 1] * inv);
+                            pw[e] = *reinterpret_cast<unsigned*>(&hh);
                         }
+                        const int piece = (ch * OC + c) / 8 + q4;
+                        *reinterpret_cast<uint4*>(stage + row * (HD * 2) + ((piece ^ (row & 7)) << 4)) = pk;
+                    }
+                }
+            }
+            pair_sync();
+            if (good) {
+                const int tid = ch * 32 + lane;                  // 0..63 among the two warps
+#pragma unroll 4
+                for (int k = 0; k < 32 * ROW_PIECES / 64; ++k) {
+                    const int idx = k * 64 + tid;
+                    const int r = quarter * 32 + idx / ROW_PIECES, piece = idx % ROW_PIECES;
+                    const int mm = mt0 + r;
+                    if (mm < M) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(stage + r * (HD * 2) + ((piece ^ (r & 7)) << 4));
+                        *reinterpret_cast<uint4*>(a.out + ((size_t)(q0 + mm / G) * a.nh + kvh * G + mm % G) * HD + piece * 8) = v;
                     }
                 }
             }
