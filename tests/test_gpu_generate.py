@@ -17,29 +17,44 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _check_greedy(plain, prompt, tokens, margin):
-    """Every generated token is the plain implementation's argmax given the tokens before it, or (for
-    bfloat16) a token whose plain logit is within `margin` of that maximum."""
-    ids = list(prompt)
+def _check_greedy(plain, prompt, tokens, dtype, rounded=None):
+    """Every generated token is the plain implementation's argmax given the tokens before it.  In bfloat16 the
+    reference is the plain implementation with bfloat16 rounding at the engine's places, and another token is
+    accepted only where that reference nearly ties: the engine's logits may lie up to `tol` from the
+    reference's (the bound of the replay tests: three quarters of the distance between the rounded and the
+    32-bit plain run, on this very sequence), so its choice can differ only where the reference's gap is at most
+    2 tol.  Returns the largest gap that was accepted."""
+    ids, worst = list(prompt), 0.0
     for t in tokens:
-        row = plain.logits(ids)[-1]
+        row = plain.logits(ids)
+        margin = 1e-4
+        if dtype == "bfloat16":
+            row16 = rounded.logits(ids)
+            margin = 2 * max(5e-3, 0.75 * float((row16 - row).abs().max()))
+            row = row16
+        row = row[-1]
         best = int(row.argmax())
-        assert t == best or float(row[best] - row[t]) <= margin, (len(ids), t, best, float(row[best] - row[t]))
+        gap = float(row[best] - row[t])
+        assert t == best or gap <= margin, (len(ids), t, best, gap, margin)
+        worst = max(worst, gap)
         ids.append(t)
+    return worst
 
 
-@pytest.mark.parametrize("dtype,margin", [("float32", 1e-4), ("bfloat16", 3e-2)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cfg,page,chunk", [(TINY_A, 16, 64), (TINY_B, 8, 48), (TINY_C, 16, 40)])
-def test_greedy_generation_through_the_entry_point(tmp_path, cfg, page, chunk, dtype, margin):
+def test_greedy_generation_through_the_entry_point(tmp_path, cfg, page, chunk, dtype):
     d = make_model_dir(str(tmp_path / "m"), cfg, 5, dtype="bfloat16", sharpen=1.5)
     llm = LLM(d, dtype=dtype, page_size=page, max_cached_tokens=1024, max_num_seqs=4, max_num_batched_tokens=64,
               prefill_chunk=chunk)
     prompts = [random_ids(n, cfg["vocab_size"], i) for i, n in enumerate([1, 5, 64, 130, 33, 7])]
     outs = llm.generate(prompts, SamplingParams(greedy=True), max_tokens=16, eos_token_id=None)
-    plain = PlainQwen3(d)
+    plain, rounded = PlainQwen3(d), PlainQwen3(d, round_to=torch.bfloat16)
+    worst = 0.0
     for p, o in zip(prompts, outs):
         assert len(o.token_ids) == 16 and o.finish_reason == "length"
-        _check_greedy(plain, p, o.token_ids, margin)
+        worst = max(worst, _check_greedy(plain, p, o.token_ids, dtype, rounded))
+    print(f"greedy {dtype}: largest gap of an accepted token to the reference's best {worst:.2e}")
     llm.engine.cache.check_invariants()
     assert not llm.engine.cache.requests
     assert llm.engine.ops.launches > 0
@@ -138,7 +153,7 @@ def test_command_line(tmp_path):
     assert lines[-1] == "[Generated 12 tokens total]"
     plain = PlainQwen3(d)
     for prompt, line in zip(([5, 17, 3], [9, 8, 7, 6]), lines):
-        _check_greedy(plain, prompt, [int(x) for x in line.split()], 1e-4)
+        _check_greedy(plain, prompt, [int(x) for x in line.split()], "float32")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -155,6 +170,6 @@ def test_requests_that_end_on_eos_at_different_steps_with_pipelined_decoding(tmp
     expected, piped, unpiped, base = eos_scenario(mk, prompts)
     assert piped == expected and unpiped == expected
     assert len({len(t) for t, _ in expected}) >= 4
-    plain = PlainQwen3(d)
+    plain, rounded = PlainQwen3(d), PlainQwen3(d, round_to=torch.bfloat16)
     for p, toks in zip(prompts, base):
-        _check_greedy(plain, p, toks, 1e-4 if dtype == "float32" else 3e-2)
+        _check_greedy(plain, p, toks, dtype, rounded)
