@@ -161,13 +161,18 @@ bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr) 
 }
 
 // Whether a plain product of this size goes to this package's tcgen05 kernel rather than to cuBLAS when the choice is
-// "auto".  The kernel walks over whole 128 x 256 tiles, one block per SM: 256 tiles on 148 SMs take the time of two
-// waves for 1.73 waves of work, and there cuBLAS, which balances such a product, is 10-15 % faster.  "auto" takes
-// the kernel when its last wave is at least 90 % full.
+// "auto".  The kernel walks over whole tiles: 256 x 256 per pair of SMs from 129 tokens and 129 columns on (128 x 256
+// or 128 x 128 per SM below that).  128 tiles on 74 pairs take the time of two waves for 1.73 waves of work, and there
+// cuBLAS, which has the same tiles but more shapes to choose from, is 4 % faster (2,048 tokens of the 8B shape: 53 / 75
+// / 153 us for the output, q|k|v and down products against 51 / 72 / 156 us; at 8,192 tokens, where the waves are
+// full, 194 / 289 / 704 us against 259 / 301 / 806 us).  "auto" takes the kernel when its last wave is at least 90 % full.
 bool tc_fills_its_waves(const LlmeExecutor& ex, int M, int N) {
-    const long long tiles = (long long)((M + 127) / 128) * ((N + (N > 128 ? 255 : 127)) / (N > 128 ? 256 : 128));
-    const long long waves = (tiles + ex.sms - 1) / ex.sms;
-    return 10 * tiles >= 9 * waves * ex.sms;
+    const bool pairs = M > 128 && N > 128;
+    const long long tiles = pairs ? (long long)((M + 255) / 256) * ((N + 255) / 256)
+                                  : (long long)((M + 127) / 128) * ((N + (N > 128 ? 255 : 127)) / (N > 128 ? 256 : 128));
+    const long long walkers = pairs ? ex.sms / 2 : ex.sms;
+    const long long waves = (tiles + walkers - 1) / walkers;
+    return 10 * tiles >= 9 * waves * walkers;
 }
 
 int cublas_product(LlmeExecutor& ex, const LlmeStep& step, const void* x, long long ldx, const void* w, long long ldw, void* out,

@@ -497,6 +497,11 @@ class CudaOps:
         self._check(lib, rc, "gemm_tcgen05")
         return out
 
+    def gemm_tc_pairing(self, how: str) -> None:
+        """Whether the tcgen05 product runs on pairs of SMs (tcgen05 with .cta_group::2, 256-row tiles): "auto" (from
+        129 tokens on), "single" (never) or "pair" (always).  For tests and measurements."""
+        self._lib("gemm_tcgen05").llme_gemm_tc_pairing(c_int({"auto": 0, "single": 1, "pair": 2}[how]))
+
     def linear_tc_status(self) -> int:
         """0 if no bounded wait of the tcgen05 kernels ever gave up (synchronises the device)."""
         return int(self._lib("gemm_tcgen05").llme_gemm_tc_status())

@@ -152,10 +152,19 @@ def test_linear_bf16_sums_in_32bit_whatever_the_shape(ops, M, N, K):
     assert ((out32.double().cpu() - want).abs() <= sums * 2e-6).all()
 
 
+@pytest.fixture(params=["single", "pair"])
+def pairing(ops, request):
+    """The tcgen05 product on single SMs (128-row tiles) and on pairs of SMs (tcgen05 with .cta_group::2, 256-row
+    tiles, each block loading half of the tile's rows of W), whatever the size."""
+    ops.gemm_tc_pairing(request.param)
+    yield request.param
+    ops.gemm_tc_pairing("auto")
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 72), (129, 257, 264), (300, 1000, 96), (2048, 520, 1024),
-                                   (1000, 4096, 4096), (257, 24, 8)])
-def test_tcgen05_gemm(ops, M, N, K, out_dtype):
+                                   (1000, 4096, 4096), (257, 24, 8), (1, 8, 8), (255, 136, 40), (513, 1032, 200)])
+def test_tcgen05_gemm(ops, pairing, M, N, K, out_dtype):
     """The prompt-portion product on the tcgen05 tensor cores: tiles that hang over every edge, one and
     many k blocks, more tiles than SMs."""
     a = _rand(M, K, dtype=torch.bfloat16, seed=50)
@@ -173,7 +182,7 @@ def test_tcgen05_gemm(ops, M, N, K, out_dtype):
         assert (got - want).abs().max() < tol
 
 
-def test_tcgen05_gemm_into_a_strided_unaligned_output(ops):
+def test_tcgen05_gemm_into_a_strided_unaligned_output(ops, pairing):
     """An output whose rows do not start on 16-byte boundaries takes the register-store epilogue."""
     a = _rand(200, 128, dtype=torch.bfloat16, seed=52)
     w = _rand(77, 128, dtype=torch.bfloat16, seed=53)
@@ -244,7 +253,7 @@ def test_skinny_gemm_with_swiglu(ops, skinny, M, inter, K):
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(2048, 4096, 4096), (2048, 2560, 520), (1500, 3000, 72), (2048, 6144, 264), (130, 40000, 128)])
-def test_tcgen05_gemm_more_tiles_than_sms(ops, M, N, K, out_dtype):
+def test_tcgen05_gemm_more_tiles_than_sms(ops, pairing, M, N, K, out_dtype):
     """More tiles than SMs and not a multiple of them: a block walks over several tiles, the last wave is partly
     empty, both accumulator buffers are in use.  The same bits every time."""
     a = _rand(M, K, dtype=torch.bfloat16, seed=54)
@@ -267,7 +276,7 @@ def test_tcgen05_gemm_more_tiles_than_sms(ops, M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("M,inter,K", [(2048, 12288, 4096), (128, 128, 64), (300, 1000, 264), (129, 72, 520), (1000, 136, 8)])
-def test_tcgen05_gemm_with_swiglu(ops, monkeypatch, M, inter, K):
+def test_tcgen05_gemm_with_swiglu(ops, monkeypatch, pairing, M, inter, K):
     """The tcgen05 product with the activation in its epilogue against the product followed by the activation
     kernel, and against 64-bit arithmetic; widths that end inside a tile."""
     monkeypatch.setattr(ops, "plain_gemm", "tcgen05")     # also at sizes that the product path gives to cuBLAS
