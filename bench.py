@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one GPU, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--shape 8b|14b|32b] [--mode decode|prefill|serve] [--no-extra] [--breakdown]
+                    [--shape 8b|14b|32b] [--mode decode|prefill|serve|sweep] [--no-extra] [--breakdown]
 
 Headline (no --shape/--mode): Qwen3-8B layer sizes, random weights, bfloat16, cache pages of 16 tokens; a decode
 step for a batch of 8 requests that each hold 2,048 cached tokens (context length 4,096: they could go on to
@@ -432,6 +432,49 @@ def run_decode_prefill(name, cfg, batches, cached, context, page, steps, warmup,
     return out
 
 
+def long_prompt_flops(cfg, T: int) -> float:
+    """A prompt of T tokens whose logits are wanted at its last place only."""
+    return prefill_flops(cfg, T)
+
+
+def run_sweep(cfg, page, steps, warmup, pk):
+    """Further sizes: decode at batch 1 / 8 / 32 over 512 to 32,768 cached tokens, and whole prompts of 256 to 32,768
+    tokens run in portions of 2,048; each as a fraction of its roofline (bytes of weights and live cache / time / copy
+    bandwidth; flops / time / burst peak)."""
+    from llmengine_b200.engine.engine import StepEntry
+    contexts, batches, prompts = [512, 2048, 8192, 32768], [1, 8, 32], [256, 1024, 2048, 8192, 32768]
+    longest = max(contexts) + 256
+    b = Bench(cfg, page, max(batches), longest, 2048, 2048)
+    torch = b.torch
+    out = dict(shape_record(cfg, cfg["num_hidden_layers"]), page_size=page, decode={}, prefill={})
+    for cached in contexts:
+        for batch in batches:
+            ms, _, ctx, _ = b.decode(batch, cached, steps, warmup)
+            ach = decode_bytes(cfg, batch, ctx) / (ms * 1e-3) / 1e9
+            out["decode"][f"ctx{cached}_b{batch}"] = {"ms": round(ms, 4), "frac": round(ach / pk["hbm_gbs"], 3)}
+    for T in prompts:
+        ids, times = b.tokens(T), []
+        for i in range(2 + 5):
+            name = f"s{b.counter}"
+            b.counter += 1
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for a in range(0, T, 2048):
+                part = ids[a:a + 2048]
+                last = a + 2048 >= T
+                b.eng.step([StepEntry(name, part, [len(part) - 1] if last else [])], end=[name] if last else [])
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        out["prefill"][f"t{T}"] = {"ms": round(ms, 3), "tokens_per_s": round(T * 1000.0 / ms, 1),
+                                   "frac": round(long_prompt_flops(cfg, T) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3)}
+    b.eng.check_kernels()
+    b.close()
+    return out
+
+
 def run_serve(cfg, page, pk):
     b = Bench(cfg, page, 32, 2048 + 256 + 64, 1024, 512, max_cached_tokens=32 * (2048 + 256 + 64))
     b.serve(4, 128, 512, 16)                      # warm-up: compiles, captures, allocates
@@ -450,7 +493,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default=None, choices=sorted(SHAPES), help="run one shape alone (with --mode)")
-    ap.add_argument("--mode", default=None, choices=["decode", "prefill", "serve"])
+    ap.add_argument("--mode", default=None, choices=["decode", "prefill", "serve", "sweep"],
+                    help="sweep: decode over 512 to 32,768 cached tokens at batch 1 / 8 / 32 and prompts of 256 to 32,768 "
+                         "tokens (give --layers 4: the full depth does not leave room for the longest contexts' cache)")
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the shape has (the record then names both numbers)")
     ap.add_argument("--batch", type=int, default=8)
@@ -482,7 +527,11 @@ def main() -> int:
         if args.layers:
             cfg["num_hidden_layers"] = args.layers
         mode = args.mode or "decode"
-        if mode == "serve":
+        if mode == "sweep":
+            rec = {"metric": f"roofline fractions at further sizes, Qwen3-{name.upper()} shape bf16",
+                   "sweep": run_sweep(cfg, PAGE_SIZE, min(args.steps, 32), args.warmup, pk)}
+            rec["value"], rec["unit"] = rec["sweep"]["decode"]["ctx2048_b8"]["frac"], "fraction of the copy bandwidth"
+        elif mode == "serve":
             rec = {"metric": f"continuous batching, Qwen3-{name.upper()} shape bf16: 32 requests, prompts 128-2048, 256 new tokens",
                    "serve": run_serve(cfg, PAGE_SIZE, pk)}
             rec["value"], rec["unit"] = rec["serve"]["generated_tokens_per_s"], "tokens/s"
