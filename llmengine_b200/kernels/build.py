@@ -143,6 +143,8 @@ def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) 
     paths = {n: library_path(n) for n in names}
     todo = [n for n in names if not os.path.exists(paths[n])]
     if not todo:
+        if _manifest_differs(paths):       # a source went back to a state whose library was still there
+            write_manifest(names)
         return paths
     nvcc = find_nvcc()
     procs = {}
@@ -185,6 +187,16 @@ def all_keys() -> List[str]:
     for v in VARIANTS.values():
         keys.extend(v)
     return keys
+
+
+def _manifest_differs(paths: Dict[str, str]) -> bool:
+    import json
+    try:
+        with open(os.path.join(build_dir(), "manifest.json"), "r", encoding="utf-8") as f:
+            known = json.load(f)
+    except (OSError, ValueError):
+        return True
+    return any(known.get(k) != os.path.basename(p) for k, p in paths.items())
 
 
 def write_manifest(more: Iterable[str] = ()) -> str:
