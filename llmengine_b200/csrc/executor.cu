@@ -149,11 +149,16 @@ constexpr int SKINNY_ROWS = 16;      // most rows the weight-streaming product t
 // against the library's product for up to 8 tokens when its blocks fill their waves (4096 rows: 256 blocks for 296
 // places, 5.5 TB/s on 4096 x 12288 against 3.1), and loses when a second wave is nearly empty (5120 rows: 320 blocks,
 // 4.5 TB/s on 5120 x 17408 against 5.6) or when 9 to 16 tokens double the operands it re-reads from L2 per block.
+// Where its waves of 296 are badly filled the kernel has a lighter form with three blocks per SM (444 places: 6.1 TB/s
+// on 5120 x 17408 / 25600, against 5.7 to 5.9 for the library); 7,168 rows (448 groups) fit neither and go to the library.
 bool skinny_pays(const LlmeExecutor& ex, int M, long long row_groups) {
     if (M > 8) return false;
     const long long places = 2LL * ex.sms, waves = (row_groups + places - 1) / places;
     if (4 * row_groups <= places) return true;          // a small product is bound by its launch, not by its waves
-    return 10 * row_groups >= 8 * waves * places;
+    if (10 * row_groups >= 8 * waves * places) return true;
+    // the kernel's lighter form, three blocks per SM: 444 places a round (gemm_skinny.cu chooses it by the same figures)
+    const long long places3 = 3LL * ex.sms, waves3 = (row_groups + places3 - 1) / places3;
+    return 10 * row_groups >= 7 * waves3 * places3;
 }
 
 bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr) {

@@ -33,7 +33,7 @@ typedef __nv_bfloat16 bf16;
 constexpr int KC = 64;            // k values per chunk (two blocks of 32)
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-constexpr int UNROLL = 4;         // chunks whose loads are issued together
+int g_dense = 0;                  // llme_gemm_skinny_dense()
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -58,8 +58,10 @@ struct SkinnyArgs {
 // MT: 8-token tiles (1: M <= 8, 2: M <= 16).  Every block of a token's row re-reads the tokens' operands from L2, so
 // beyond 16 tokens that traffic outgrows the weights' and the library product is faster (measured at 17 to 32 tokens:
 // 2.1 to 3.6 TB/s against 4.1 to 5.2 TB/s).
-template <int MT, typename O>
-__global__ void __launch_bounds__(THREADS, 2) gemm_skinny_kernel(SkinnyArgs a) {
+// UNROLL: chunks of K whose loads a warp issues together; BLOCKS: blocks that must fit an SM (2 with 4 chunks in flight,
+// 3 with 2: fewer bytes in flight per SM, but 444 places instead of 296 for the row groups of a product).
+template <int MT, typename O, int UNROLL, int BLOCKS>
+__global__ void __launch_bounds__(THREADS, BLOCKS) gemm_skinny_kernel(SkinnyArgs a) {
     __shared__ float red[WARPS][MT * 8][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int quad = lane & 3, r = lane >> 2;
@@ -167,10 +169,29 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_skinny_kernel(SkinnyArgs a) {
     }
 }
 
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) v = 148;
+        return v;
+    }();
+    return n;
+}
+
 template <int MT, typename O>
 int launch(const SkinnyArgs& a, cudaStream_t s) {
     const int groups = a.inter > 0 ? (a.inter + 7) / 8 : (a.N + 15) / 16;
-    llme_launch(gemm_skinny_kernel<MT, O>, dim3(groups), dim3(THREADS), 0, s, a);
+    // Two blocks per SM (296 places) keep the most bytes in flight.  Row groups that fill their rounds of 296 badly
+    // but rounds of 444 well (6,144 rows: 384 groups; 5,120 rows: 320; 10,240 rows: 640) go to three lighter blocks
+    // per SM: measured at 8 tokens, 5120 x 25600 takes 42.9 us against 56.9 us (cuBLAS 44.6), 6144 x 4096 10.6
+    // against 11.0 (cuBLAS 11.1); with 256 groups, which fit one round either way, the lighter blocks lose (9.0
+    // against 8.2 us).  The executor's choice between this kernel and the library uses the same two figures.
+    const long long p2 = 2LL * sm_count(), p3 = 3LL * sm_count();
+    const long long w2 = (groups + p2 - 1) / p2 * p2, w3 = (groups + p3 - 1) / p3 * p3;          // places of the rounds taken
+    const bool fills2 = 10LL * groups >= 8 * w2, fills3 = 10LL * groups >= 7 * w3;
+    const bool dense = MT == 1 && (g_dense == 2 || (g_dense == 0 && !fills2 && fills3 && 4LL * groups > p2));
+    if (dense) llme_launch(gemm_skinny_kernel<MT, O, 2, 3>, dim3(groups), dim3(THREADS), 0, s, a);
+    else llme_launch(gemm_skinny_kernel<MT, O, 4, 2>, dim3(groups), dim3(THREADS), 0, s, a);
     LLME_LAUNCH_STATUS();
 }
 
@@ -180,6 +201,12 @@ int dispatch(const SkinnyArgs& a, cudaStream_t s) {
 }
 
 }  // namespace
+
+// 0 (the default): three lighter blocks per SM where the row groups then fit one round; 1: never; 2: always (up to 8 tokens).
+LLME_API int llme_gemm_skinny_dense(int how) {
+    if (how >= 0 && how <= 2) g_dense = how;
+    return g_dense;
+}
 
 // 1 if llme_gemm_skinny_bf16 takes this problem, 0 if the caller should use the general product.
 LLME_API int llme_gemm_skinny_supports(int M, int N, int K, long long ldx, long long ldw) {
