@@ -272,15 +272,16 @@ class Engine:
 
     @property
     def takes_device_tokens(self) -> bool:
-        """Whether `step(..., device_tokens=...)` is served (one cache group that keeps all positions)."""
-        return len(self.cache.groups) == 1 and not self.cache.groups[0].window
+        """Whether `step(..., device_tokens=...)` is served: by every model (any number of cache groups, with or
+        without a window, with or without state slots)."""
+        return True
 
     def _decode_step(self, entries, end, device_tokens=None):
         """The common case made cheap on the host: every entry is one token of a live request that wants
         its logits.  Same checks and same effects as the general path, computed with whole-batch array
         operations instead of per-request ones.  Returns NotImplemented when the batch is of another kind."""
         R = len(entries)
-        if R == 0 or R > self._R_cap or len(self.cache.groups) != 1 or self.cache.groups[0].window:
+        if R == 0 or R > self._R_cap:
             return NotImplemented
         reqs = self.cache.requests
         states = []
@@ -301,16 +302,16 @@ class Engine:
         if lengths.max() + 1 > self.max_model_len:
             return NotImplemented
         slots = np.fromiter((st.slot for st in states), dtype=np.int64, count=R)
-        g = self.cache.groups[0]
-        ps = g.page_size
-        grow = np.nonzero(lengths % ps == 0)[0]            # these requests step onto a new page
-        if grow.size:
-            if any(len(states[i].blocks[0]) * ps <= lengths[i] for i in grow):
-                need = sum(1 for i in grow if len(states[i].blocks[0]) * ps <= lengths[i])
-                if need > g.pool.free_count:
-                    return NotImplemented                  # the general path raises the error and undoes nothing
-                for i in grow:
-                    self.cache.reserve(entries[i].request, int(lengths[i]) + 1)
+        groups = self.cache.groups
+        growing = set()
+        for gi, g in enumerate(groups):
+            grow = np.nonzero(lengths % g.page_size == 0)[0]       # these requests step onto a new page of this group
+            short = [int(i) for i in grow if len(states[i].blocks[gi]) * g.page_size <= lengths[i]]
+            if len(short) > g.pool.free_count:
+                return NotImplemented                      # the general path raises the error and undoes nothing
+            growing.update(short)
+        for i in sorted(growing):
+            self.cache.reserve(entries[i].request, int(lengths[i]) + 1)
         i = self.steps & 1
         if self._staging_ev[i] is not None and self._staging_used[i]:
             self._staging_ev[i].synchronize()
@@ -319,7 +320,9 @@ class Engine:
         h[off["token_ids"]][:R] = toks
         h[off["positions"]][:R] = lengths
         h[off["token_request"]][:R] = slots
-        h[off["slot_mapping0"]][:R] = self.cache.tables[0][slots, lengths // ps].astype(np.int64) * ps + lengths % ps
+        for gi, g in enumerate(groups):
+            ps = g.page_size
+            h[off[f"slot_mapping{gi}"]][:R] = self.cache.tables[gi][slots, lengths // ps].astype(np.int64) * ps + lengths % ps
         h[off["logit_rows"]][:R] = ar
         h[off["cu_q_lens"]][:R + 1] = np.arange(R + 1, dtype=np.int32)
         h[off["ctx_lens"]][:R] = lengths + 1
@@ -340,17 +343,22 @@ class Engine:
 
         if device_tokens is not None:
             torch.index_select(device_tokens[0], 0, view("portion_rows", R), out=view("token_ids", R))
-        group = GroupView(ps, 0, self.cache.tables_dev[0], view("slot_mapping0", R), g.max_blocks)
+        views = [GroupView(g.page_size, g.window, self.cache.tables_dev[gi], view(f"slot_mapping{gi}", R), g.max_blocks)
+                 for gi, g in enumerate(groups)]
         batch = StepBatch(
             num_tokens=R, num_requests=R, q_lens=[1] * R, start_positions=lengths.tolist(),
             token_ids=view("token_ids", R), positions=view("positions", R), token_request=view("token_request", R),
             cu_q_lens=view("cu_q_lens", R + 1), ctx_lens=view("ctx_lens", R), state_slots=view("state_slots", R),
             first_portion=view("first_portion", R), logit_rows=view("logit_rows", R),
-            decode_rows=view("decode_rows", R), portion_rows=view("portion_rows", 0), groups=[group])
+            decode_rows=view("decode_rows", R), portion_rows=view("portion_rows", 0), groups=views)
         self.cache.flush()
         logits = self._forward(batch)
-        for st in states:
-            st.length += 1
+        if any(g.window for g in groups):
+            for e, n in zip(entries, lengths):             # pages that a window has passed go back
+                self.cache.advance(e.request, int(n) + 1)
+        else:
+            for st in states:
+                st.length += 1
         self.steps += 1
         for r in end:
             self.cache.free_request(r)

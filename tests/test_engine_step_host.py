@@ -97,3 +97,30 @@ def test_a_good_step_still_works_after_refusals(engine):
     assert out.shape == (2, engine.vocab)
     assert not engine.cache.has("a") and engine.cache.length("b") == 23
     engine.cache.check_invariants()
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_the_host_cheap_decode_path_does_what_the_general_one_does(tmp_path, name):
+    """Steps of single tokens take a path that works on whole arrays; forced through the general path instead, the
+    same requests give the same logits and leave the same tables, free lists and lengths, step after step: across
+    page edges, and in C while the window of one cache group gives pages back."""
+    cfg = {"A": TINY_A, "C": TINY_C}[name]
+    d = make_model_dir(str(tmp_path / "m"), cfg, 4, dtype="float32")
+    engines = [engine_for(d, "float32", 256, page_size=8, ops=HostOps(), device="cpu", max_requests=3) for _ in range(2)]
+    engines[1]._decode_step = lambda entries, end, device_tokens=None: NotImplemented
+    ids = {"a": random_ids(70, cfg["vocab_size"], 1), "b": random_ids(45, cfg["vocab_size"], 2)}
+    outs = []
+    for eng in engines:
+        got = [eng.step([StepEntry("a", ids["a"][:20], [19])])]
+        for i in range(45):
+            entries = [StepEntry("a", ids["a"][20 + i:21 + i], [0]), StepEntry("b", ids["b"][i:i + 1], [0])]
+            if i == 0:
+                entries[1] = StepEntry("b", ids["b"][:1], [0])          # b's first token: a new request, the general path
+            got.append(eng.step(entries, end=["b"] if i == 44 else []))
+            eng.cache.check_invariants()
+        outs.append(got)
+    for x, y in zip(*outs):
+        assert np.array_equal(x.numpy(), y.numpy())
+    _same(_snapshot(engines[0]), _snapshot(engines[1]))
+    if name == "C":
+        assert any(p == -1 for p in engines[0].cache.requests["a"].blocks[1]), "the window gave no page back"

@@ -60,14 +60,15 @@ def test_greedy_generation_through_the_entry_point(tmp_path, cfg, page, chunk, d
     assert llm.engine.ops.launches > 0
 
 
+@pytest.mark.parametrize("cfg", [TINY_B, TINY_C], ids=["B", "C"])
 @pytest.mark.parametrize("short_context", [8192, 48])
-def test_cuda_graph_decoding_gives_the_same_tokens(tmp_path, monkeypatch, short_context):
+def test_cuda_graph_decoding_gives_the_same_tokens(tmp_path, monkeypatch, short_context, cfg):
     """Captured decode steps against eager ones; with the small limit the requests grow past it while they decode,
     so that both kinds of capture (short contexts, any context) are made and replayed."""
     from llmengine_b200.engine.engine import Engine
     monkeypatch.setattr(Engine, "SHORT_CONTEXT", short_context)
-    d = make_model_dir(str(tmp_path / "m"), TINY_B, 8, dtype="bfloat16", sharpen=1.5)
-    prompts = [random_ids(n, 1000, i) for i, n in enumerate([9, 40, 3])]
+    d = make_model_dir(str(tmp_path / "m"), cfg, 8, dtype="bfloat16", sharpen=1.5)
+    prompts = [random_ids(n, cfg["vocab_size"], i) for i, n in enumerate([9, 40, 3])]
     runs = []
     for graphs in (False, True):
         llm = LLM(d, dtype="bfloat16", page_size=8, max_cached_tokens=1024, max_num_seqs=4, max_num_batched_tokens=64,

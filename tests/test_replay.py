@@ -264,12 +264,13 @@ def test_a_wrong_page_is_seen_at_the_tolerance_of_the_replay_tests(tmp_path, nam
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("short_context", [8192, 48])
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_logits_of_captured_decode_steps(tmp_path, monkeypatch, name, dtype, short_context):
     """Decode steps replayed from CUDA graphs give the plain implementation's logits: most of each request in one
     step and its last 32 tokens one by one, and a long run of single-token steps of two requests side by side.  With
     the small limit the requests grow past it while they decode, so both kinds of capture (launch shapes for short
-    contexts, and for any context) are made and replayed."""
+    contexts, and for any context) are made and replayed.  Configuration C has two cache groups, one of them with a
+    window whose pages go back while the requests decode, and a layer order that runs a layer twice."""
     from llmengine_b200.engine.engine import Engine
     monkeypatch.setattr(Engine, "SHORT_CONTEXT", short_context)
     d, page, reqs, ref, tol = _setup(tmp_path, name, dtype, 2.0)
