@@ -40,7 +40,9 @@
 // hold it (16 bytes a lane, every lane another row) cost 1.4 us a block, 3 to 4 us of the launch; through shared
 // memory it is whole rows.  With O_t(i) and S_t(i+1) as separate rounds of eight, each with waits and commits of its
 // own: 62.7 us.  One Q tile per block with P in shared memory took 71 us.  A second issuing warp (one per Q tile)
-// made it slower (66.8 us).
+// made it slower (66.8 us).  One softmax thread a row (four warps a Q tile, nothing exchanged between threads, the
+// next 32 scores on their way from tensor memory while 32 are worked on): 56.3 us; a thread's 128 exponentials
+// in a row leave the two warps a scheduler then has too little to overlap.
 //
 // Also tried and dropped, each correct and each slower (62 to 65 us): one block per SM that walks a list of
 // 128-row items (queries and probabilities in tensor memory, four threads a row, the scores one or two key tiles
