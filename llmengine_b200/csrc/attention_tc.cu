@@ -42,7 +42,9 @@
 // own: 62.7 us.  One Q tile per block with P in shared memory took 71 us.  A second issuing warp (one per Q tile)
 // made it slower (66.8 us).  One softmax thread a row (four warps a Q tile, nothing exchanged between threads, the
 // next 32 scores on their way from tensor memory while 32 are worked on): 56.3 us; a thread's 128 exponentials
-// in a row leave the two warps a scheduler then has too little to overlap.
+// in a row leave the two warps a scheduler then has too little to overlap.  Every fourth exponential as a cubic on the
+// FMA units (range reduction through the exponent bits, relative error 1e-4) instead of the special-function unit:
+// 56.6 us; the softmax warps are short of issue slots, not of exponentials.
 //
 // Also tried and dropped, each correct and each slower (62 to 65 us): one block per SM that walks a list of
 // 128-row items (queries and probabilities in tensor memory, four threads a row, the scores one or two key tiles
