@@ -668,7 +668,6 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
     }
     __syncthreads();
 
-    pdl_launch_dependents();
     // merge the four warps' partial results in shared memory, in a fixed order
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -914,7 +913,9 @@ static int launch_decode(const FastAttnArgs& a, const FusedQkv& f, cudaStream_t 
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = llme_pdl_enabled() ? 1 : 0;
+        // no programmatic dependent launch for the clustered form: next to it the kernels before and after lose
+        // 6 to 8 us each (common.cuh); nor does the kernel let its successor in before it has finished
+        attr[0].val.programmaticStreamSerializationAllowed = 0;
         attr[1].id = cudaLaunchAttributeClusterDimension;
         attr[1].val.clusterDim.x = (unsigned)a.splits;
         attr[1].val.clusterDim.y = 1;

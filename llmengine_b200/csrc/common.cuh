@@ -44,15 +44,14 @@ inline char* llme_error_buffer() {
 // kernel has started); what it reads from or writes to memory that the earlier kernel touches must come
 // after pdl_wait(), which returns when the earlier kernel has completed.  Work that does not depend on
 // it (reading weights) may come first.  pdl_launch_dependents() lets the next kernel be scheduled early.
-// Both are no-ops for kernels launched the ordinary way.  It is off unless LLME_PDL=1 is set in the
-// environment: measured inside CUDA graphs on B200 (Qwen3-8B shape, batch 8) the decode step took 5.1 ms
-// with it (6.7 ms when every kernel let its successor in at its very start) and 3.85 ms without: the
-// early-resident successors take issue slots and bandwidth from the kernel on the critical path.  Switched
-// on for the kernels of single source files or single products it stayed within the noise of the step time
-// (+-0.7%), except for the output product after the decode attention, which lost 7 us.  Measured again pair by pair
-// (a layer's operations in a graph, batch 8): every transition between products and norms gains 0.1 to 0.9 us, the
-// two around the decode attention (whose splits are launched as clusters) lose 8.3 and 5.9 us, and a whole layer
-// takes 133 us against 95 us.
+// Both are no-ops for kernels launched the ordinary way.  It is on unless LLME_PDL=0 is set in the environment,
+// for every kernel but the decode attention whose splits are launched as thread-block clusters.  Measured inside
+// CUDA graphs on B200 (Qwen3-8B shape, batch 8), a layer's operations pair by pair: every transition between
+// products and norms gains 0.1 to 0.9 us, but the two around the clustered decode attention lose 8.3 and 5.9 us
+// when it takes part (a layer then needs 133 us against 95 us, a step 5.1 ms against 3.85 ms; 6.7 ms when every
+// kernel let its successor in at its very start).  With that kernel left out a layer takes 90.4 us, a decode step
+// at batch 8 3.48 ms against 3.55 ms, a step of 121 prompt tokens beside 7 decoded ones 5.7 ms against 6.1 ms; the
+// GPU tests pass either way.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -62,7 +61,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 inline bool llme_pdl_enabled() {
     static const bool on = [] {
         const char* e = getenv("LLME_PDL");
-        return e && e[0] == '1';
+        return !(e && e[0] == '0');
     }();
     return on;
 }
