@@ -502,6 +502,11 @@ class CudaOps:
         129 tokens on), "single" (never) or "pair" (always).  For tests and measurements."""
         self._lib("gemm_tcgen05").llme_gemm_tc_pairing(c_int({"auto": 0, "single": 1, "pair": 2}[how]))
 
+    def gemm_skinny_form(self, how: str) -> None:
+        """The weight-streaming product with two blocks an SM ("two"), in its lighter form with three ("three", up to 8
+        tokens) or as the kernel chooses by how its row groups fill their rounds ("auto").  For tests and measurements."""
+        self._lib("gemm_skinny").llme_gemm_skinny_dense(c_int({"auto": 0, "two": 1, "three": 2}[how]))
+
     def linear_tc_status(self) -> int:
         """0 if no bounded wait of the tcgen05 kernels ever gave up (synchronises the device)."""
         return int(self._lib("gemm_tcgen05").llme_gemm_tc_status())

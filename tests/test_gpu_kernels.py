@@ -20,11 +20,14 @@ def ops():
     return CudaOps(torch.device(DEV))
 
 
-@pytest.fixture
-def skinny(ops):
-    """The weight-streaming product also for shapes that the executor's own choice would give to the library."""
+@pytest.fixture(params=["two blocks an SM", "three blocks an SM", "as the kernel chooses"])
+def skinny(ops, request):
+    """The weight-streaming product also for shapes that the executor's own choice would give to the library, in its
+    form with two blocks an SM, in its lighter form with three (up to 8 tokens), and as it chooses itself."""
     ops.choose("linear.decode", "skinny")
+    ops.gemm_skinny_form({"two blocks an SM": "two", "three blocks an SM": "three", "as the kernel chooses": "auto"}[request.param])
     yield ops
+    ops.gemm_skinny_form("auto")
     ops.choose("linear.decode", "auto")
 
 
