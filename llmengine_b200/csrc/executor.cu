@@ -303,13 +303,15 @@ int op_qkv_post(LlmeExecutor& ex, const LlmeQkvPostOp& o, const LlmeStep& s, cud
 // Blocks per (request, key/value head) of the decode attention: as many as fit the GPU in one wave (two blocks per
 // SM), never more than there are 64-key groups in the longest (windowed) context.  Up to 8 splits run as one
 // thread-block cluster and merge through shared memory, which is worth more than a finer split while a block's share
-// stays short (measured at batch 1 and 2,048 keys: 8.3 us with 8 splits, 8.9 us with 16, 11 us with 32).
+// stays short (measured at batch 1 and 2,048 keys: 8.3 us with 8 splits, 8.9 us with 16, 11 us with 32).  Beyond 16
+// splits the adding-up of the parts by the block that finishes last costs more than the finer split brings (batch 1,
+// 8,200 keys: 15.1 us with 16 splits, 16.9 us with 37, 23.2 us with 64; 32,768 keys: 32.5 / 33.2 / 37.7 us).
 int decode_splits(const LlmeExecutor& ex, int requests, int nh, int nkv, int window, long long max_ctx) {
     const long long span = window > 0 && window < max_ctx ? window : max_ctx;
     const long long groups = (span + 63) / 64 + (window > 0 ? 1 : 0);
     const int G = nh / nkv;
     const long long blocks = (long long)requests * nkv * ((G + 15) / 16);
-    long long splits = groups < 64 ? groups : 64;
+    long long splits = groups < 16 ? groups : 16;
     if (2LL * ex.sms / blocks < splits) splits = 2LL * ex.sms / blocks;
     if (splits < 1) splits = 1;
     if (splits > 8 && span <= 8 * 1024) splits = 8;
