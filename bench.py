@@ -503,6 +503,8 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
     ap.add_argument("--no-extra", "--skip-points", dest="no_extra", action="store_true",
                     help="the headline only: no further page size, shapes or probes")
+    ap.add_argument("--behind", type=int, default=0,
+                    help="with --breakdown: the timed prompt portion lies behind this many cached tokens of its request")
     ap.add_argument("--breakdown", action="store_true",
                     help="instead of the bench line, print the time of every operation of a layer (decode at --batch "
                          "inside a CUDA graph, and a 2,048-token prefill), timed with CUDA events")

@@ -16,8 +16,9 @@ def breakdown(args, model_cfg, CACHED, CONTEXT, PREFILL_TOKENS, pk) -> int:
     cfg = dict(model_cfg)
     cfg["num_hidden_layers"] = min(args.layers or 12, 12)
     B, T = args.batch, PREFILL_TOKENS
-    ec = EngineConfig(dtype="bfloat16", page_size=args.page_size, max_cached_tokens=B * CONTEXT + T, max_num_seqs=B + 1,
-                      max_num_batched_tokens=T, max_model_len=CONTEXT, use_cuda_graphs=False)
+    behind = max(0, int(getattr(args, "behind", 0) or 0))          # tokens the prompt's request already holds
+    ec = EngineConfig(dtype="bfloat16", page_size=args.page_size, max_cached_tokens=B * CONTEXT + T + behind, max_num_seqs=B + 1,
+                      max_num_batched_tokens=T, max_model_len=max(CONTEXT, behind + T), use_cuda_graphs=False)
     eng = Engine(config=cfg, random_seed=0, engine_config=ec)
     gen = torch.Generator().manual_seed(0)
     names = [f"r{i}" for i in range(B)]
@@ -87,15 +88,21 @@ def breakdown(args, model_cfg, CACHED, CONTEXT, PREFILL_TOKENS, pk) -> int:
     print(f"| **sum** | **{total:.1f}** | | |\n\nAttention reads {kv / 1e6:.1f} MB of cache per layer; "
           f"the layer's weights are {layer_weights / 1e6:.0f} MB: at the peak "
           f"bandwidth the layer would take {(layer_weights + kv) / pk['hbm_gbs'] / 1e3:.1f} us.\n")
-    eng.cache.add_request("prefill")
-    eng.cache.reserve("prefill", T)
-    pre = eng._build_batch([StepEntry("prefill", torch.randint(0, 1000, (T,), generator=gen).tolist(), [T - 1])], [0])
+    if behind:
+        ids = torch.randint(0, 1000, (behind,), generator=gen).tolist()
+        for a in range(0, behind, T):
+            eng.step([StepEntry("prefill", ids[a:a + T], [])])
+    else:
+        eng.cache.add_request("prefill")
+    eng.cache.reserve("prefill", behind + T)
+    pre = eng._build_batch([StepEntry("prefill", torch.randint(0, 1000, (T,), generator=gen).tolist(), [T - 1])], [behind])
     eng.cache.flush()
     rows, total = table(pre, True)
-    print(f"## Prefill of one {T}-token prompt\n")
+    print(f"## Prefill of one {T}-token prompt\n" if not behind else
+          f"## A {T}-token portion of a prompt behind {behind} cached tokens\n")
     print("| operation | us per layer | TFLOP/s | share |\n|---|---|---|---|")
     for name, us, w in rows:
-        fl = 2.0 * T * w if w else (4.0 * nh * hd * T * (T + 1) / 2 if "attention" in name and "rmsnorm" not in name else 0)
+        fl = 2.0 * T * w if w else (4.0 * nh * hd * (T * behind + T * (T + 1) / 2) if "attention" in name and "rmsnorm" not in name else 0)
         print(f"| {name} | {us:.1f} | {('%.0f' % (fl / us / 1e6)) if fl else ''} | {100 * us / total:.0f}% |")
     print(f"| **sum** | **{total:.0f}** | | |")
     eng.check_kernels()
