@@ -17,7 +17,10 @@ OUT = os.path.join(HERE, "_ref")
 BINARY = os.path.join(OUT, "reference_bench")
 
 
-def build(reference: str = "/root/reference") -> str:
+DEFAULT_REFERENCE = os.environ.get("LLME_REFERENCE", os.path.join(os.path.expanduser("~"), "reference"))
+
+
+def build(reference: str = DEFAULT_REFERENCE) -> str:
     if not os.path.exists(os.path.join(reference, "CMakeLists.txt")):
         raise RuntimeError(f"the reference's sources are not at {reference}")
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
