@@ -509,8 +509,13 @@ __device__ __forceinline__ void norm_rotate_head(const bf16* src, const void* ga
 }
 
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs a, FusedQkv f) {
-    // (the next kernel is let in just before the merge below, not here: it would compete with the key/value stream)
-    pdl_wait();                // everything below reads or writes what earlier kernels touch
+    // Launched while the kernel before it is still running (programmatic dependent launch), the kernel may read, before
+    // pdl_wait(), only what that kernel does not write.  Taking the raw projections (f.qkv), it follows the product
+    // that made them: the step's lengths and tables and the keys and values of earlier positions are older than that
+    // product, so the block table and the first key/value loads need not wait for it; the projections do.  Otherwise
+    // the kernel before it has written the cache, and everything waits.
+    const bool early_loads = f.qkv != nullptr;
+    if (!early_loads) pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][LDS]
     bf16* stages = Qs + 16 * LDS;                              // [4 warps][DSTAGES][K 16 rows | V 16 rows][LDS]
@@ -591,7 +596,10 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
     };
     // With few sub-tiles the first loads below may already fetch the new token's position: then it is stored first.
     const bool store_early = writer && my_last - my_first < 4 * (DSTAGES - 1);
+    bool waited = !early_loads;
     if (store_early) {
+        if (!waited) pdl_wait();           // the new key and value come from the projections
+        waited = true;
         store_new_kv();
         __threadfence_block();
         __syncthreads();
@@ -617,6 +625,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
             if (sub <= my_last) load_sub_tile(mine + st * STAGE_ELEMS, a.cache, tab, tab_first, kvh, a.nkv, ps, page_shift, sub * SUB, lo, p);
             cp_async_commit();
         }
+        if (!waited) pdl_wait();           // the first key/value loads are under way: now the projections
+        waited = true;
         if (f.qkv) {
             // the query heads from the raw projection: a warp per head; rows beyond the group's heads are zeros
             for (int row = warp; row < 16; row += 4) {
@@ -666,6 +676,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(FastAttnArgs 
         }
         cp_async_wait<0>();
     }
+    if (!waited) pdl_wait();               // a block without a share of the context: before it writes anything
     __syncthreads();
 
     // merge the four warps' partial results in shared memory, in a fixed order
@@ -913,9 +924,10 @@ static int launch_decode(const FastAttnArgs& a, const FusedQkv& f, cudaStream_t 
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        // no programmatic dependent launch for the clustered form: next to it the kernels before and after lose
-        // 6 to 8 us each (common.cuh); nor does the kernel let its successor in before it has finished
-        attr[0].val.programmaticStreamSerializationAllowed = 0;
+        // the kernel may begin while the product before it runs (its block table and first key/value loads do not
+        // wait for it), but it never lets its successor in before it has finished: that cost the kernels around it 7
+        // to 10 us (common.cuh)
+        attr[0].val.programmaticStreamSerializationAllowed = llme_pdl_enabled() ? 1 : 0;
         attr[1].id = cudaLaunchAttributeClusterDimension;
         attr[1].val.clusterDim.x = (unsigned)a.splits;
         attr[1].val.clusterDim.y = 1;

@@ -44,15 +44,14 @@ inline char* llme_error_buffer() {
 // kernel has started); what it reads from or writes to memory that the earlier kernel touches must come
 // after pdl_wait(), which returns when the earlier kernel has completed.  Work that does not depend on
 // it (reading weights) may come first.  pdl_launch_dependents() lets the next kernel be scheduled early.
-// Both are no-ops for kernels launched the ordinary way.  It is on unless LLME_PDL=0 is set in the environment,
-// for every kernel but the decode attention whose splits are launched as thread-block clusters.  Measured inside
-// CUDA graphs on B200 (Qwen3-8B shape, batch 8), a layer's operations pair by pair: every transition between
-// products and norms gains 0.1 to 0.9 us, but the two around the clustered decode attention lose 8.3 and 5.9 us
-// when it takes part (a layer then needs 133 us against 95 us, a step 5.1 ms against 3.85 ms; 6.7 ms when every
-// kernel let its successor in at its very start).  With that kernel left out a layer takes 90.4 us, a decode step
-// at batch 8 3.48 ms against 3.55 ms, a step of 121 prompt tokens beside 7 decoded ones 5.7 ms against 6.1 ms; the
-// GPU tests pass either way.  (It is the kernel's letting its successor in early that costs: with that alone put back,
-// the kernel itself launched the ordinary way, the two transitions lose 10 and 7 us again.)
+// Both are no-ops for kernels launched the ordinary way.  It is on unless LLME_PDL=0 is set in the environment.
+// Measured inside CUDA graphs on B200 (Qwen3-8B shape, batch 8), a layer's operations pair by pair: every transition
+// between products and norms gains 0.1 to 0.9 us.  The decode attention may begin early (its block table and first
+// key/value loads come before its pdl_wait(): 1.1 us), but must not let its successor in before it has finished: with
+// pdl_launch_dependents() before its merge, the transitions before and after it lose 10 and 7 us (a layer then needs
+// 132 us against 95 us without any of this, a step 5.1 ms against 3.85 ms; 6.7 ms when every kernel let its successor
+// in at its very start).  As it is now a layer takes 89.8 us, a decode step at batch 8 3.45 ms against 3.55 ms, a step of
+// 121 prompt tokens beside 7 decoded ones 5.7 ms against 6.1 ms; the GPU tests pass either way.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
