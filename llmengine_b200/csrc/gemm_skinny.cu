@@ -113,6 +113,11 @@ __global__ void __launch_bounds__(THREADS, BLOCKS) gemm_skinny_kernel(SkinnyArgs
             }
         }
         if (first) {
+            // The next kernel may be scheduled from here on: its blocks move in as this kernel's leave (this kernel's
+            // blocks fill the SMs' registers, so nothing of it is displaced), and its own first loads, or its tables,
+            // are under way when this kernel ends.  (A layer's operations at batch 8 take 88.2 us so, 89.8 us with
+            // the successor let in only before this kernel's short epilogue.)
+            pdl_launch_dependents();
             pdl_wait();
             first = false;
         }
@@ -137,7 +142,6 @@ __global__ void __launch_bounds__(THREADS, BLOCKS) gemm_skinny_kernel(SkinnyArgs
     }
     if (first) pdl_wait();
 
-    pdl_launch_dependents();   // only the short epilogue is left: the next kernel may move in
     // the warps' partial sums, added in a fixed order: value (token, row) at index token * 16 + row
 #pragma unroll
     for (int m = 0; m < MT; ++m)
