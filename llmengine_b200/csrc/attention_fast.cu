@@ -879,6 +879,36 @@ LLME_API long long llme_attention_decode_scratch_floats(int n_rows, int nh, int 
     return splits <= 1 ? 0 : (long long)COUNTER_WORDS + (long long)n_rows * nh * splits * PART;
 }
 
+// How many clusters of `splits` blocks of the decode kernel the GPU holds at once (0: unknown).  A cluster's blocks
+// must find room in one GPC together, so this is less than the blocks the SMs hold divided by the cluster's size.
+LLME_API int llme_attention_decode_clusters(int splits) {
+    if (splits < 2 || splits > 8) return 0;
+    static int known[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    if (known[splits]) return known[splits];
+    if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)splits, 1024, 1);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = DECODE_SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    known[splits] = n;
+    return n;
+}
+
 LLME_API int llme_attention_portion(const FastAttnArgs* args, int max_q_len, cudaStream_t stream) {
     const FastAttnArgs& a = *args;
     if (a.n_rows <= 0 || max_q_len <= 0) return 0;

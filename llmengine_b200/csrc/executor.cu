@@ -152,8 +152,11 @@ constexpr int SKINNY_ROWS = 16;      // most rows the weight-streaming product t
 // Where its waves of 296 are badly filled the kernel has a lighter form with three blocks per SM (444 places: 6.1 TB/s
 // on 5120 x 17408 / 25600, against 5.7 to 5.9 for the library); 7,168 rows (448 groups) fit neither and go to the library.
 bool skinny_pays(const LlmeExecutor& ex, int M, long long row_groups) {
-    if (M > 8) return false;
     const long long places = 2LL * ex.sms, waves = (row_groups + places - 1) / places;
+    // 9 to 16 tokens: only where the row groups are one well-filled round (4,096 rows: 256 groups).  There the kernel
+    // takes 8.0 / 20.0 us for 4096 x 4096 / 4096 x 12288 against 10.6 / 21.7 us; with more row groups, each re-reading
+    // the tokens' operands, the library is ahead (6144 x 4096: 14.3 against 12.9 us; 24576 x 4096: 39.5 against 37.7).
+    if (M > 8) return row_groups <= places && 10 * row_groups >= 8 * places;
     if (4 * row_groups <= places) return true;          // a small product is bound by its launch, not by its waves
     if (10 * row_groups >= 8 * waves * places) return true;
     // the kernel's lighter form, three blocks per SM: 444 places a round (gemm_skinny.cu chooses it by the same figures)
@@ -300,22 +303,38 @@ int op_qkv_post(LlmeExecutor& ex, const LlmeQkvPostOp& o, const LlmeStep& s, cud
     return ex.launched(f(&a, o.in_dtype, o.out_dtype, st), "qkv_post");
 }
 
-// Blocks per (request, key/value head) of the decode attention: as many as fit the GPU in one wave (two blocks per
-// SM), never more than there are 64-key groups in the longest (windowed) context.  Up to 8 splits run as one
-// thread-block cluster and merge through shared memory, which is worth more than a finer split while a block's share
-// stays short (measured at batch 1 and 2,048 keys: 8.3 us with 8 splits, 8.9 us with 16, 11 us with 32).  Beyond 16
-// splits the adding-up of the parts by the block that finishes last costs more than the finer split brings (batch 1,
-// 8,200 keys: 15.1 us with 16 splits, 16.9 us with 37, 23.2 us with 64; 32,768 keys: 32.5 / 33.2 / 37.7 us).
-int decode_splits(const LlmeExecutor& ex, int requests, int nh, int nkv, int window, long long max_ctx) {
+// Blocks per (request, key/value head) of the decode attention, chosen by what the kernel's time is made of.  A block
+// streams its share of the keys at a rate of its own (about 27 GB/s: its warps' loads wait for one another), and
+// needs about 6 us beside that, the time of some 300 keys; the blocks run in rounds of as many as the GPU holds at
+// once.  Up to 8 splits are one thread-block cluster and merge through shared memory; the blocks of a cluster must find
+// room in one GPC together, so the GPU holds fewer clusters than its SMs hold blocks (71 of four blocks, not 74; 93 of
+// three, not 98: the kernel library says how many), and one cluster too many is a second round: 9 requests of 8
+// key/value heads in clusters of four took 33 us a layer against 17 us for 8 requests, 19 us in clusters of three.
+// More than 8 splits (at most 16) merge through scratch memory, where the block that finishes last adds the parts up,
+// the dearer the more there are (batch 1, 8,200 keys: 15.1 us with 16 splits, 16.9 us with 37, 23.2 us with 64).
+// Measured choices this reproduces: batch 1 / 8 / 9 / 12 / 16 / 24 / 40 at 2,048 keys: 8 / 4 / 3 / 2 / 2 / 1 / 3 splits.
+typedef int (*AttnClustersFn)(int);
+
+int decode_splits(const LlmeExecutor& ex, int requests, int nh, int nkv, int hd, int window, long long max_ctx) {
     const long long span = window > 0 && window < max_ctx ? window : max_ctx;
-    const long long groups = (span + 63) / 64 + (window > 0 ? 1 : 0);
+    const long long groups = (span + 63) / 64 + (window > 0 ? 1 : 0);      // 64-key groups of the longest context
     const int G = nh / nkv;
-    const long long blocks = (long long)requests * nkv * ((G + 15) / 16);
-    long long splits = groups < 16 ? groups : 16;
-    if (2LL * ex.sms / blocks < splits) splits = 2LL * ex.sms / blocks;
-    if (splits < 1) splits = 1;
-    if (splits > 8 && span <= 8 * 1024) splits = 8;
-    return (int)splits;
+    const long long units = (long long)requests * nkv * ((G + 15) / 16);     // (request, key/value head, 16 query heads)
+    auto* room = (AttnClustersFn)ex.find_hd("attention_decode_clusters", hd);
+    long long best = 1, best_cost = -1;
+    for (long long s = 1; s <= 16 && s <= groups; ++s) {
+        long long held = 2LL * ex.sms;                                       // blocks the GPU holds at once
+        if (s >= 2 && s <= 8 && room) {
+            const int clusters = room((int)s);
+            if (clusters > 0) held = s * clusters;
+        }
+        const long long rounds = (units * s + held - 1) / held;
+        const long long keys = (groups + s - 1) / s * 64;
+        const long long fixed = s <= 8 ? 300 : 300 + 25 * s;
+        const long long cost = rounds * (keys + fixed) * (100 + 8 * (rounds - 1));      // later rounds are never quite full
+        if (best_cost < 0 || cost < best_cost) { best = s; best_cost = cost; }
+    }
+    return (int)best;
 }
 
 bool fast_attention(LlmeExecutor& ex, int dtype, int hd) {
@@ -367,7 +386,7 @@ int op_attend(LlmeExecutor& ex, const LlmeAttendOp& o, const LlmeStep& s, cudaSt
         }
     }
     if (s.num_decode > 0) {
-        const int splits = decode_splits(ex, s.num_decode, o.nh, o.nkv, o.window, s.max_decode_ctx);
+        const int splits = decode_splits(ex, s.num_decode, o.nh, o.nkv, o.hd, o.window, s.max_decode_ctx);
         if (int rc = scratch_check(ex, o, s.num_decode, splits)) return rc;
         LlmeFastAttnArgs a = {};
         fill_fast(a, o, s, s.decode_rows, s.num_decode, splits);
@@ -386,7 +405,7 @@ int op_attention(LlmeExecutor& ex, const LlmeAttentionOp& o, const LlmeStep& s, 
         s.num_decode == s.num_tokens && at.hd % 4 == 0 && o.qkv_stride % 2 == 0 &&
         (((uintptr_t)o.qkv | (uintptr_t)o.post.q_gain | (uintptr_t)o.post.k_gain | (uintptr_t)o.post.cos_sin) & 7) == 0) {
         if (at.group < 0 || at.group >= s.num_groups) return ex.fail("attention: the step has no cache group %d", at.group);
-        const int splits = decode_splits(ex, s.num_decode, at.nh, at.nkv, at.window, s.max_decode_ctx);
+        const int splits = decode_splits(ex, s.num_decode, at.nh, at.nkv, at.hd, at.window, s.max_decode_ctx);
         if (int rc = scratch_check(ex, at, s.num_decode, splits)) return rc;
         LlmeFastAttnArgs a = {};
         fill_fast(a, at, s, s.decode_rows, s.num_decode, splits);
@@ -478,16 +497,16 @@ LLME_EXPORT const char* llme_executor_chosen(LlmeExecutor* ex, const char* op) {
 LLME_EXPORT const char* llme_executor_error(LlmeExecutor* ex) { return ex->error.c_str(); }
 LLME_EXPORT long long llme_executor_launches(LlmeExecutor* ex) { return ex->launches; }
 
-LLME_EXPORT int llme_decode_splits(LlmeExecutor* ex, int requests, int nh, int nkv, int window, int max_ctx) {
+LLME_EXPORT int llme_decode_splits(LlmeExecutor* ex, int requests, int nh, int nkv, int hd, int window, int max_ctx) {
     if (requests <= 0 || nh <= 0 || nkv <= 0 || nh % nkv) return 1;
-    return decode_splits(*ex, requests, nh, nkv, window, max_ctx);
+    return decode_splits(*ex, requests, nh, nkv, hd, window, max_ctx);
 }
 
 LLME_EXPORT long long llme_attention_scratch_floats(LlmeExecutor* ex, int max_requests, int nh, int nkv, int hd) {
     if (max_requests <= 0 || nh <= 0 || nkv <= 0 || nh % nkv) return 0;
     long long most = 0;
     for (int n = 1; n <= max_requests; ++n) {
-        const int splits = decode_splits(*ex, n, nh, nkv, 0, 1LL << 30);
+        const int splits = decode_splits(*ex, n, nh, nkv, hd, 0, 1LL << 30);
         const long long need = splits <= 1 ? 0 : 65536 + (long long)n * nh * splits * (hd + 2);
         if (need > most) most = need;
     }

@@ -648,6 +648,7 @@ private:
             reg(lib, ("attention_decode/" + hd).c_str(), "llme_attention_decode");
             reg(lib, ("attention_decode_fused/" + hd).c_str(), "llme_attention_decode_fused");
             reg(lib, ("attention_decode_scratch/" + hd).c_str(), "llme_attention_decode_scratch_floats");
+            reg(lib, ("attention_decode_clusters/" + hd).c_str(), "llme_attention_decode_clusters");
             if (cfg_.head_dim == 64 || cfg_.head_dim == 128) reg("attention_tc@HEAD_DIM=" + hd, ("attention_tc/" + hd).c_str(), "llme_attention_tc");
         } else {
             reg("attention_plain", "attention_plain", "llme_attention_plain");

@@ -155,7 +155,7 @@ long long llme_executor_launches(LlmeExecutor*);      /* kernels of this package
 /* Scratch floats an attention record needs for steps of up to `max_requests` single tokens. */
 long long llme_attention_scratch_floats(LlmeExecutor*, int max_requests, int nh, int nkv, int hd);
 /* Blocks per (request, key/value head) that the decode attention would use. */
-int llme_decode_splits(LlmeExecutor*, int requests, int nh, int nkv, int window, int max_ctx);
+int llme_decode_splits(LlmeExecutor*, int requests, int nh, int nkv, int hd, int window, int max_ctx);
 
 LlmePlan* llme_plan_create(LlmeExecutor*);
 void llme_plan_destroy(LlmePlan*);

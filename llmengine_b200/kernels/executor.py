@@ -100,7 +100,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.llme_executor_launches.argtypes = [c_void_p]
     lib.llme_attention_scratch_floats.restype = c_longlong
     lib.llme_attention_scratch_floats.argtypes = [c_void_p, c_int, c_int, c_int, c_int]
-    lib.llme_decode_splits.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int]
+    lib.llme_decode_splits.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int]
     lib.llme_plan_create.restype = c_void_p
     lib.llme_plan_create.argtypes = [c_void_p]
     lib.llme_plan_destroy.argtypes = [c_void_p]

@@ -170,8 +170,8 @@ class CudaOps:
     def attention_scratch_floats(self, max_requests: int, num_heads: int, num_kv_heads: int, head_dim: int) -> int:
         return int(self._xlib.llme_attention_scratch_floats(self._ex, max_requests, num_heads, num_kv_heads, head_dim))
 
-    def decode_splits(self, requests: int, num_heads: int, num_kv_heads: int, window: int, max_ctx: int) -> int:
-        return int(self._xlib.llme_decode_splits(self._ex, requests, num_heads, num_kv_heads, window, max_ctx))
+    def decode_splits(self, requests: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, max_ctx: int) -> int:
+        return int(self._xlib.llme_decode_splits(self._ex, requests, num_heads, num_kv_heads, head_dim, window, max_ctx))
 
     _ENTRY_POINTS = {
         "elementwise": {"embedding": "llme_embedding", "rmsnorm": "llme_rmsnorm", "qkv_post": "llme_qkv_post",
@@ -182,7 +182,8 @@ class CudaOps:
         "attention_plain": {"attention_plain": "llme_attention_plain"},
         "attention_fast": {"attention_portion/{hd}": "llme_attention_portion", "attention_decode/{hd}": "llme_attention_decode",
                            "attention_decode_fused/{hd}": "llme_attention_decode_fused",
-                           "attention_decode_scratch/{hd}": "llme_attention_decode_scratch_floats"},
+                           "attention_decode_scratch/{hd}": "llme_attention_decode_scratch_floats",
+                           "attention_decode_clusters/{hd}": "llme_attention_decode_clusters"},
         "attention_tc": {"attention_tc/{hd}": "llme_attention_tc"},
     }
 
