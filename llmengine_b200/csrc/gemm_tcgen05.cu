@@ -323,7 +323,22 @@ int launch_kernel(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMa
         configured = true;
     }
     const int tiles = a.m_tiles * a.n_tiles;
-    const int walkers = PAIR ? sm_count() / 2 : sm_count();               // blocks, or pairs of blocks
+    int walkers = PAIR ? sm_count() / 2 : sm_count();                     // blocks, or pairs of blocks
+    if (PAIR) {
+        // The two blocks of a pair need two free SMs of one GPC: a GPU may hold fewer pairs than half its SMs.  A pair
+        // that had to wait for another to finish would double the kernel's time, so there are never more than fit.
+        static int held = 0;
+        if (!held) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * 1024, 1, 1);
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = smem;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = walkers; }
+            held = n;
+        }
+        if (held < walkers) walkers = held;
+    }
     const int grid = (tiles < walkers ? tiles : walkers) * (PAIR ? 2 : 1);
     kernel<<<grid, THREADS, smem, s>>>(mx, mw, mo, a);
     LLME_LAUNCH_STATUS();
